@@ -1,0 +1,152 @@
+/*
+ * minfer_attn.h — C ABI of the sm_100a attention library (libminfer_attn.so).
+ *
+ * Plain pointers and sizes only: no torch types cross this boundary.  Every
+ * pointer named "device" must be a CUDA device pointer valid on the current
+ * device; `stream` is a cudaStream_t passed as void*.  All entry points are
+ * asynchronous with respect to the host (they enqueue work on `stream` and
+ * return) and allocate no device memory: the caller owns inputs, outputs and
+ * the optional workspace.
+ *
+ * Return value: 0 on success, otherwise one of the MINFER_ATTN_E* codes;
+ * minfer_attn_strerror() gives a one-line description.  The library never
+ * falls back to a CPU path; without a usable sm_100 device calls fail.
+ *
+ * Reference interface this replaces (dsuarez01/minfer-python):
+ *   src/minfer/kernels/torch_ext/csrc/cuda/flash_attn/op.cuh:21-106
+ *     (flash_attn_cuda: argument validation, stride capture, stream fetch,
+ *      then an unimplemented launch)
+ *   src/minfer/kernels/torch_ext/csrc/cuda/flash_attn/kernels/kernel.cuh:11-27
+ *     (QKVStrides, HALF_MIN, the empty flash_attn_cuda_impl kernel)
+ */
+#ifndef MINFER_ATTN_H_
+#define MINFER_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MINFER_ATTN_ABI_VERSION 1
+
+/* element types of q/k/v/out */
+#define MINFER_ATTN_F16  0
+#define MINFER_ATTN_BF16 1
+
+/* error codes */
+#define MINFER_ATTN_OK            0
+#define MINFER_ATTN_EINVAL        1  /* bad shape / stride / pointer / dtype        */
+#define MINFER_ATTN_EUNSUPPORTED  2  /* valid request this build has no kernel for  */
+#define MINFER_ATTN_ECUDA         3  /* a CUDA runtime / driver call failed          */
+#define MINFER_ATTN_ENODEVICE     4  /* current device is not compute capability 10 */
+#define MINFER_ATTN_EWORKSPACE    5  /* workspace missing or too small              */
+
+/*
+ * Prefill attention:  out = softmax(q k^T * scale + mask) v  with grouped-query
+ * heads (kv head of query head h is h / (n_heads / n_kv_heads), i.e. the
+ * repeat_interleave expansion the reference's callers apply before SDPA,
+ * test/kernels.py:253-255).
+ *
+ * Layout: q,out are [batch, n_heads, seq_q, head_dim]; k,v are
+ * [batch, n_kv_heads, seq_k, head_dim].  The innermost stride is 1; the three
+ * outer strides are given in ELEMENTS, exactly the QKVStrides fields of
+ * kernel.cuh:12-15 (the reference passes transposed views, so the strides are
+ * arbitrary; each must be a multiple of 8 elements and the base pointers must
+ * be 16-byte aligned).  k and v share one stride triple as op.cuh:46-48 demands.
+ *
+ * mask: NULL, or a contiguous [batch, 1, seq_q, seq_k] array of bytes where a
+ * non-zero byte means "attend" (the reference's bool mask, op.cuh:28,50).
+ * causal != 0 applies j <= i + (seq_k - seq_q) instead and ignores `mask`.
+ * A row with no visible key yields zeros.
+ *
+ * softmax_scale == 0 selects 1/sqrt(head_dim) (the SDPA default used by
+ * refs.py:55).  head_dim is 64 or 128.
+ *
+ * status: optional device int32[4].  A kernel that gives up a bounded wait
+ * writes {code, blockIdx.x, blockIdx.y, site} there; it is never written on
+ * success.  The caller zeroes it and reads it after synchronising.
+ */
+typedef struct MinferAttnPrefillParams {
+  const void*    q;
+  const void*    k;
+  const void*    v;
+  void*          out;
+  const uint8_t* mask;
+  int32_t*       status;
+  int64_t q_stride[3];    /* elements: batch, head, row */
+  int64_t kv_stride[3];
+  int64_t out_stride[3];
+  int32_t batch;
+  int32_t n_heads;
+  int32_t n_kv_heads;
+  int32_t seq_q;
+  int32_t seq_k;
+  int32_t head_dim;
+  int32_t dtype;          /* MINFER_ATTN_F16 / MINFER_ATTN_BF16 */
+  int32_t causal;
+  float   softmax_scale;
+  int32_t flags;          /* reserved, pass 0 */
+} MinferAttnPrefillParams;
+
+int minfer_attn_prefill(const MinferAttnPrefillParams* params, void* stream);
+
+/*
+ * Decode attention over a padded KV cache (one query token per sequence).
+ * No counterpart exists in the reference: its op insists on seq_q == seq_k
+ * (op.cuh:76).  The cache layout is the one the reference's model skeleton
+ * allocates, [batch, n_kv_heads, max_seq_len, head_dim] (src/minfer/core.py:105-127).
+ *
+ * q,out: [batch, n_heads, 1, head_dim] with element strides for batch and head.
+ * k_cache,v_cache: [batch, n_kv_heads, max_len, head_dim], element strides for
+ * batch, head, row; innermost stride 1.  lens: device int32[batch], sequence b
+ * attends keys [0, lens[b]); entries beyond lens[b] are never read.  A
+ * sequence with lens[b] == 0 yields zeros.
+ *
+ * The KV range of a sequence is cut into chunks of `chunk` keys, each handled
+ * by its own thread block (split-KV); partial results go through `workspace`,
+ * a device buffer of at least minfer_attn_decode_workspace_bytes() bytes that
+ * the caller owns.  chunk == 0 lets the library choose; otherwise it must be a
+ * positive multiple of 64.
+ */
+typedef struct MinferAttnDecodeParams {
+  const void*    q;
+  const void*    k_cache;
+  const void*    v_cache;
+  const int32_t* lens;
+  void*          out;
+  void*          workspace;
+  size_t         workspace_bytes;
+  int64_t q_stride[2];    /* elements: batch, head */
+  int64_t kv_stride[3];   /* elements: batch, head, row */
+  int64_t out_stride[2];
+  int32_t batch;
+  int32_t n_heads;
+  int32_t n_kv_heads;
+  int32_t max_len;
+  int32_t head_dim;
+  int32_t dtype;
+  int32_t chunk;
+  float   softmax_scale;
+} MinferAttnDecodeParams;
+
+int minfer_attn_decode(const MinferAttnDecodeParams* params, void* stream);
+
+/* Bytes of workspace minfer_attn_decode() needs for this shape and chunk
+ * (chunk == 0: the library's own choice).  Returns 0 for invalid arguments. */
+size_t minfer_attn_decode_workspace_bytes(int32_t batch, int32_t n_heads,
+                                          int32_t max_len, int32_t head_dim,
+                                          int32_t chunk);
+
+/* The chunk minfer_attn_decode() uses when params->chunk == 0. */
+int32_t minfer_attn_decode_default_chunk(int32_t batch, int32_t n_kv_heads,
+                                         int32_t max_len);
+
+const char* minfer_attn_strerror(int code);
+int minfer_attn_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MINFER_ATTN_H_ */

@@ -1,0 +1,86 @@
+"""Build libminfer_attn.so (the C-ABI attention library) for sm_100a, in-tree.
+
+Replaces the reference's setup.py CUDAExtension build
+(setup.py:19-86 of dsuarez01/minfer-python, which targets compute_89 and asserts
+a GPU at build time): one `nvcc -shared` over the three translation units, one
+target architecture, no GPU needed to build.
+
+Usage:  python build.py [--force] [--verbose]
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+INCLUDE = os.path.join(os.path.dirname(HERE), "include")
+OUT_DIR = os.path.join(HERE, "minfer", "kernels", "torch_ext")
+LIB_NAME = "libminfer_attn.so"
+SOURCES = ["attn_api.cu", "prefill_sm100.cu", "decode_sm100.cu"]
+HEADERS = ["attn_internal.h", "ptx.cuh"]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "-Xcompiler", "-fPIC",
+    "--expt-relaxed-constexpr",
+]
+
+
+def lib_path() -> str:
+    return os.path.join(OUT_DIR, LIB_NAME)
+
+
+def _newest_source_mtime() -> float:
+    files = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
+    files.append(os.path.join(INCLUDE, "minfer_attn.h"))
+    return max(os.path.getmtime(f) for f in files)
+
+
+def _find_nvcc() -> str:
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise RuntimeError("nvcc not found; libminfer_attn.so cannot be built")
+    return nvcc
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile if the library is missing or older than its sources; return its path."""
+    out = lib_path()
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= _newest_source_mtime():
+        return out
+    nvcc = _find_nvcc()
+    objs = []
+    build_dir = os.path.join(HERE, "build")
+    os.makedirs(build_dir, exist_ok=True)
+    procs = []
+    for src in SOURCES:
+        obj = os.path.join(build_dir, src.replace(".cu", ".o"))
+        cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-c", os.path.join(CSRC, src), "-o", obj]
+        if verbose:
+            cmd.insert(1, "-Xptxas")
+            cmd.insert(2, "-v")
+            print(" ".join(cmd), flush=True)
+        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        objs.append(obj)
+    for src, p in procs:
+        log, _ = p.communicate()
+        if verbose or p.returncode != 0:
+            sys.stdout.write(log)
+        if p.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}")
+    cmd = [nvcc, "-shared", "-o", out, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static"]
+    subprocess.run(cmd, check=True)
+    return out
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--verbose", action="store_true")
+    ns = ap.parse_args()
+    print(build(force=ns.force, verbose=ns.verbose))

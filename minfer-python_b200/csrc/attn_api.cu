@@ -1,0 +1,227 @@
+// C-ABI layer of libminfer_attn.so: argument validation, TMA tensor-map
+// construction and kernel launches.  Mirrors the checks of the reference's
+// launcher (src/minfer/kernels/torch_ext/csrc/cuda/flash_attn/op.cuh:32-103)
+// on plain pointers and sizes.
+#include "../../include/minfer_attn.h"
+#include "attn_internal.h"
+
+#include <algorithm>
+#include <cmath>
+#include <mutex>
+
+namespace minfer_attn {
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Is the current device compute capability 10.x?  Cached per device.
+int check_device() {
+  static int cached[64] = {};  // 0 unknown, 1 ok, 2 wrong arch
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return MINFER_ATTN_ECUDA;
+  if (dev < 64 && cached[dev] != 0) return cached[dev] == 1 ? MINFER_ATTN_OK : MINFER_ATTN_ENODEVICE;
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return MINFER_ATTN_ECUDA;
+  if (dev < 64) cached[dev] = (major == 10) ? 1 : 2;
+  return major == 10 ? MINFER_ATTN_OK : MINFER_ATTN_ENODEVICE;
+}
+
+// Tensor map over a [batch, heads, rows, head_dim] 16-bit tensor with element
+// strides (s_b, s_h, s_r, 1).  The three outer dimensions are ordered by
+// ascending stride; pos[] receives the coordinate slot (1..3) of batch, head
+// and row.  Box = 64 elements x 128 rows, 128-byte swizzle, zero fill.
+int make_tensor_map(CUtensorMap* tm, const void* base, bool bf16, int head_dim, int64_t batch, int64_t heads,
+                    int64_t rows, const int64_t stride[3], int32_t pos[3]) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return MINFER_ATTN_ECUDA;
+  struct Dim {
+    int64_t size, stride;
+    int which;
+  } dims[3] = {{batch, stride[0], 0}, {heads, stride[1], 1}, {rows, stride[2], 2}};
+  // a dimension of extent 1 may carry any stride; give it one that encodes
+  int64_t span = head_dim;
+  for (auto& d : dims)
+    if (d.size > 1) span = std::max<int64_t>(span, d.size * d.stride);
+  for (auto& d : dims)
+    if (d.size == 1) d.stride = span;
+  std::stable_sort(dims, dims + 3, [](const Dim& x, const Dim& y) { return x.stride < y.stride; });
+  cuuint64_t gdim[4] = {static_cast<cuuint64_t>(head_dim), 0, 0, 0};
+  cuuint64_t gstr[3];
+  cuuint32_t box[4] = {64, 1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  for (int i = 0; i < 3; ++i) {
+    gdim[i + 1] = static_cast<cuuint64_t>(dims[i].size);
+    gstr[i] = static_cast<cuuint64_t>(dims[i].stride) * 2;
+    pos[dims[i].which] = i + 1;
+    if (dims[i].which == 2) box[i + 1] = 128;
+  }
+  CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                   const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MINFER_ATTN_OK : MINFER_ATTN_EINVAL;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+bool strides_ok(const int64_t* s, int n) {
+  for (int i = 0; i < n; ++i)
+    if (s[i] < 0 || (s[i] % 8) != 0) return false;
+  return true;
+}
+
+int32_t default_chunk(int32_t batch, int32_t n_kv_heads, int32_t max_len) {
+  (void)batch;
+  (void)n_kv_heads;
+  int32_t c = 512;
+  while (c > 64 && c >= 2 * max_len) c >>= 1;
+  return c;
+}
+
+}  // namespace
+}  // namespace minfer_attn
+
+using namespace minfer_attn;
+
+extern "C" {
+
+int minfer_attn_abi_version(void) { return MINFER_ATTN_ABI_VERSION; }
+
+const char* minfer_attn_strerror(int code) {
+  switch (code) {
+    case MINFER_ATTN_OK: return "ok";
+    case MINFER_ATTN_EINVAL: return "invalid argument (shape, stride, alignment, dtype or null pointer)";
+    case MINFER_ATTN_EUNSUPPORTED: return "unsupported configuration (head_dim must be 64 or 128, group <= 16)";
+    case MINFER_ATTN_ECUDA: return "a CUDA runtime or driver call failed";
+    case MINFER_ATTN_ENODEVICE: return "current CUDA device is not compute capability 10.x (sm_100)";
+    case MINFER_ATTN_EWORKSPACE: return "decode workspace missing or too small";
+    default: return "unknown error code";
+  }
+}
+
+int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
+  if (p == nullptr || p->q == nullptr || p->k == nullptr || p->v == nullptr || p->out == nullptr)
+    return MINFER_ATTN_EINVAL;
+  if (p->batch <= 0 || p->n_heads <= 0 || p->n_kv_heads <= 0 || p->seq_q <= 0 || p->seq_k <= 0)
+    return MINFER_ATTN_EINVAL;
+  if (p->n_heads % p->n_kv_heads != 0) return MINFER_ATTN_EINVAL;
+  if (p->dtype != MINFER_ATTN_F16 && p->dtype != MINFER_ATTN_BF16) return MINFER_ATTN_EINVAL;
+  if (p->head_dim != 64 && p->head_dim != 128) return MINFER_ATTN_EUNSUPPORTED;
+  if (p->causal && p->seq_k < p->seq_q) return MINFER_ATTN_EINVAL;
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return MINFER_ATTN_EINVAL;
+  if (!strides_ok(p->q_stride, 3) || !strides_ok(p->kv_stride, 3) || !strides_ok(p->out_stride, 3))
+    return MINFER_ATTN_EINVAL;
+  if (!(p->softmax_scale >= 0.f)) return MINFER_ATTN_EINVAL;
+  if (p->batch > 65535 || p->n_heads > 65535) return MINFER_ATTN_EUNSUPPORTED;
+  int rc = check_device();
+  if (rc != MINFER_ATTN_OK) return rc;
+
+  const bool bf16 = p->dtype == MINFER_ATTN_BF16;
+  PrefillArgs a{};
+  alignas(64) CUtensorMap tq, tk, tv;
+  rc = make_tensor_map(&tq, p->q, bf16, p->head_dim, p->batch, p->n_heads, p->seq_q, p->q_stride, a.q_pos);
+  if (rc != MINFER_ATTN_OK) return rc;
+  rc = make_tensor_map(&tk, p->k, bf16, p->head_dim, p->batch, p->n_kv_heads, p->seq_k, p->kv_stride, a.kv_pos);
+  if (rc != MINFER_ATTN_OK) return rc;
+  int32_t vpos[3];
+  rc = make_tensor_map(&tv, p->v, bf16, p->head_dim, p->batch, p->n_kv_heads, p->seq_k, p->kv_stride, vpos);
+  if (rc != MINFER_ATTN_OK) return rc;
+
+  a.out = p->out;
+  a.mask = p->causal ? nullptr : p->mask;
+  a.status = p->status;
+  for (int i = 0; i < 3; ++i) a.out_stride[i] = p->out_stride[i];
+  a.batch = p->batch;
+  a.n_heads = p->n_heads;
+  a.seq_q = p->seq_q;
+  a.seq_k = p->seq_k;
+  a.group = p->n_heads / p->n_kv_heads;
+  a.causal = p->causal ? 1 : 0;
+  a.mask_vec = (a.mask != nullptr && aligned16(a.mask) && (p->seq_k % 16) == 0) ? 1 : 0;
+  const float scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->head_dim));
+  a.scale_log2 = scale * 1.4426950408889634f;
+
+  cudaError_t e = launch_prefill(tq, tk, tv, a, p->head_dim, bf16, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MINFER_ATTN_OK : MINFER_ATTN_ECUDA;
+}
+
+int32_t minfer_attn_decode_default_chunk(int32_t batch, int32_t n_kv_heads, int32_t max_len) {
+  if (batch <= 0 || n_kv_heads <= 0 || max_len <= 0) return 0;
+  return default_chunk(batch, n_kv_heads, max_len);
+}
+
+size_t minfer_attn_decode_workspace_bytes(int32_t batch, int32_t n_heads, int32_t max_len, int32_t head_dim,
+                                          int32_t chunk) {
+  if (batch <= 0 || n_heads <= 0 || max_len <= 0 || (head_dim != 64 && head_dim != 128)) return 0;
+  if (chunk == 0) chunk = default_chunk(batch, 1, max_len);
+  if (chunk < 64 || chunk % 64 != 0) return 0;
+  const size_t n_split = (static_cast<size_t>(max_len) + chunk - 1) / chunk;
+  return static_cast<size_t>(batch) * n_heads * n_split * (static_cast<size_t>(head_dim) + 2) * sizeof(float);
+}
+
+int minfer_attn_decode(const MinferAttnDecodeParams* p, void* stream) {
+  if (p == nullptr || p->q == nullptr || p->k_cache == nullptr || p->v_cache == nullptr || p->lens == nullptr ||
+      p->out == nullptr)
+    return MINFER_ATTN_EINVAL;
+  if (p->batch <= 0 || p->n_heads <= 0 || p->n_kv_heads <= 0 || p->max_len <= 0) return MINFER_ATTN_EINVAL;
+  if (p->n_heads % p->n_kv_heads != 0) return MINFER_ATTN_EINVAL;
+  if (p->dtype != MINFER_ATTN_F16 && p->dtype != MINFER_ATTN_BF16) return MINFER_ATTN_EINVAL;
+  if (p->head_dim != 64 && p->head_dim != 128) return MINFER_ATTN_EUNSUPPORTED;
+  const int group = p->n_heads / p->n_kv_heads;
+  if (group > 16) return MINFER_ATTN_EUNSUPPORTED;
+  if (!aligned16(p->q) || !aligned16(p->k_cache) || !aligned16(p->v_cache) || !aligned16(p->out))
+    return MINFER_ATTN_EINVAL;
+  if (!strides_ok(p->q_stride, 2) || !strides_ok(p->kv_stride, 3) || !strides_ok(p->out_stride, 2))
+    return MINFER_ATTN_EINVAL;
+  if (!(p->softmax_scale >= 0.f)) return MINFER_ATTN_EINVAL;
+  if (p->batch > 65535 || p->n_kv_heads > 65535) return MINFER_ATTN_EUNSUPPORTED;
+  int32_t chunk = p->chunk;
+  if (chunk == 0) chunk = default_chunk(p->batch, p->n_kv_heads, p->max_len);
+  if (chunk < 64 || chunk % 64 != 0) return MINFER_ATTN_EINVAL;
+  const size_t need = minfer_attn_decode_workspace_bytes(p->batch, p->n_heads, p->max_len, p->head_dim, chunk);
+  if (p->workspace == nullptr || p->workspace_bytes < need || !aligned16(p->workspace)) return MINFER_ATTN_EWORKSPACE;
+  int rc = check_device();
+  if (rc != MINFER_ATTN_OK) return rc;
+
+  DecodeArgs a{};
+  a.q = p->q;
+  a.k = p->k_cache;
+  a.v = p->v_cache;
+  a.lens = p->lens;
+  a.out = p->out;
+  a.batch = p->batch;
+  a.n_heads = p->n_heads;
+  a.n_kv_heads = p->n_kv_heads;
+  a.max_len = p->max_len;
+  a.group = group;
+  a.chunk = chunk;
+  a.n_split = (p->max_len + chunk - 1) / chunk;
+  a.part_o = static_cast<float*>(p->workspace);
+  a.part_ml = a.part_o + static_cast<size_t>(p->batch) * p->n_heads * a.n_split * p->head_dim;
+  for (int i = 0; i < 2; ++i) {
+    a.q_stride[i] = p->q_stride[i];
+    a.out_stride[i] = p->out_stride[i];
+  }
+  for (int i = 0; i < 3; ++i) a.kv_stride[i] = p->kv_stride[i];
+  const float scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->head_dim));
+  a.scale_log2 = scale * 1.4426950408889634f;
+
+  cudaError_t e = launch_decode(a, p->head_dim, p->dtype == MINFER_ATTN_BF16, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MINFER_ATTN_OK : MINFER_ATTN_ECUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,56 @@
+// Internal declarations shared by the C-ABI layer and the kernels.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace minfer_attn {
+
+// value a kernel writes to status[0] when a bounded wait runs out
+constexpr int32_t kStatusWaitTimeout = 100;
+
+// Kernel-side view of a prefill call (tensor maps travel separately).
+struct PrefillArgs {
+  void* out;
+  const uint8_t* mask;
+  int32_t* status;
+  int64_t out_stride[3];  // elements: batch, head, row
+  int32_t batch, n_heads, seq_q, seq_k;
+  int32_t group;          // query heads per kv head
+  int32_t causal;
+  int32_t mask_vec;       // mask rows may be read with 16-byte loads
+  float scale_log2;       // softmax scale * log2(e)
+  // position (1..3) of the batch / head / row coordinate inside each tensor
+  // map; coordinate 0 is always head_dim
+  int32_t q_pos[3];
+  int32_t kv_pos[3];
+};
+
+size_t prefill_smem_bytes(int head_dim);
+cudaError_t launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillArgs& a,
+                           int head_dim, bool bf16, cudaStream_t stream);
+
+// Kernel-side view of a decode call.
+struct DecodeArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  const int32_t* lens;
+  void* out;
+  float* part_o;   // [batch, n_heads, n_split, head_dim] fp32, unnormalised
+  float* part_ml;  // [batch, n_heads, n_split, 2] running max (log2 domain) and sum
+  int64_t q_stride[2];
+  int64_t kv_stride[3];
+  int64_t out_stride[2];
+  int32_t batch, n_heads, n_kv_heads, max_len;
+  int32_t group;
+  int32_t chunk;    // keys per thread block
+  int32_t n_split;  // ceil(max_len / chunk)
+  float scale_log2;
+};
+
+cudaError_t launch_decode(const DecodeArgs& a, int head_dim, bool bf16, cudaStream_t stream);
+
+}  // namespace minfer_attn

@@ -1,0 +1,312 @@
+// Split-KV decode attention over a padded KV cache, HBM-bound.
+//
+// The reference has no decode op (its attention op requires seq_q == seq_k,
+// src/minfer/kernels/torch_ext/csrc/cuda/flash_attn/op.cuh:76); the cache
+// layout [batch, n_kv_heads, max_len, head_dim] is the one its model skeleton
+// allocates (src/minfer/core.py:105-127).
+//
+// Kernel 1 (decode_split_kernel): grid (n_split, n_kv_heads, batch).  A thread
+// block streams `chunk` keys of one (sequence, kv head) and serves all `group`
+// query heads of that kv head at once, so every cache byte is read once.  Each
+// warp runs a private cp.async ring of 16-key tiles (128-bit loads, rows of the
+// cache are contiguous, so a warp instruction covers whole 256/128-byte rows)
+// and keeps its own online-softmax state; the grouped query heads occupy the
+// 16 rows of m16n8k16 tensor-core tiles so the arithmetic stays far below the
+// memory time.  The warps' states are merged through shared memory and written
+// as one fp32 partial (max, sum, unnormalised output) per (query head, split).
+//
+// Kernel 2 (decode_combine_kernel): grid (n_heads, batch) merges the partials
+// of the ceil(len / chunk) splits of a sequence and writes the 16-bit output.
+#include "attn_internal.h"
+#include "ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace minfer_attn {
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kStages = 3;
+constexpr int kTileKeys = 16;
+
+template <int D>
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+  // 16-byte chunk index -> swizzled byte offset inside a [16 x D] 16-bit tile
+  if constexpr (D == 128) return row * 256 + (((chunk & 8) | ((chunk ^ row) & 7)) << 4);
+  else return row * 128 + (((chunk ^ row) & 7) << 4);
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kWarps * 32, 2) decode_split_kernel(const DecodeArgs a) {
+  constexpr int kRowBytes = D * 2;
+  constexpr int kTileBytes = kTileKeys * kRowBytes;        // one of K or V
+  constexpr int kChunksPerRow = D / 8;                     // 16-byte chunks
+  constexpr int kLoadsPerLane = kTileKeys * kChunksPerRow / 32;
+  constexpr int kWarpBytes = kStages * 2 * kTileBytes;
+
+  extern __shared__ __align__(128) uint8_t smem[];
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int b = blockIdx.z;
+
+  const int len = min(a.lens[b], a.max_len);
+  const int c0 = split * a.chunk;
+  if (c0 >= len) return;
+  const int c1 = min(len, c0 + a.chunk);
+  const int nt = (c1 - c0 + kTileKeys - 1) / kTileKeys;
+  const int nt_w = (nt > warp) ? (nt - warp + kWarps - 1) / kWarps : 0;
+
+  uint8_t* wsm = smem + warp * kWarpBytes;
+  const uint32_t wsm_u32 = smem_u32(wsm);
+  const uint8_t* kbase = reinterpret_cast<const uint8_t*>(a.k) +
+                         2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(kvh) * a.kv_stride[1]);
+  const uint8_t* vbase = reinterpret_cast<const uint8_t*>(a.v) +
+                         2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(kvh) * a.kv_stride[1]);
+  const size_t row_stride_bytes = 2 * static_cast<size_t>(a.kv_stride[2]);
+
+  auto issue_tile = [&](int i) {  // i-th tile of this warp -> stage i % kStages
+    if (i < nt_w) {
+      const int key0 = c0 + (warp + i * kWarps) * kTileKeys;
+      uint8_t* dst_k = wsm + (i % kStages) * 2 * kTileBytes;
+      uint8_t* dst_v = dst_k + kTileBytes;
+#pragma unroll
+      for (int t = 0; t < kLoadsPerLane; ++t) {
+        const int idx = t * 32 + lane;
+        const int row = idx / kChunksPerRow;
+        const int chunk = idx % kChunksPerRow;
+        const int key = key0 + row;
+        const bool pred = key < c1;
+        const size_t goff = static_cast<size_t>(pred ? key : c0) * row_stride_bytes + chunk * 16;
+        cp_async_16(dst_k + swz<D>(row, chunk), kbase + goff, pred);
+        cp_async_16(dst_v + swz<D>(row, chunk), vbase + goff, pred);
+      }
+    }
+    cp_async_commit();
+  };
+
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) issue_tile(s);
+
+  // ---- Q fragments: rows = query heads of this kv head (zero beyond group) ----
+  const int g0 = lane >> 2;
+  const int tq = lane & 3;
+  uint32_t qf[D / 16][4];
+  {
+    const uint8_t* qb = reinterpret_cast<const uint8_t*>(a.q) + 2 * static_cast<size_t>(b) * a.q_stride[0];
+    const int h0 = kvh * a.group + g0;
+    const int h1 = h0 + 8;
+    const uint8_t* q0p = qb + 2 * static_cast<size_t>(h0) * a.q_stride[1];
+    const uint8_t* q1p = qb + 2 * static_cast<size_t>(h1) * a.q_stride[1];
+    const bool v0 = g0 < a.group;
+    const bool v1 = g0 + 8 < a.group;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int d = ks * 16 + tq * 2;
+      qf[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0p + 2 * d) : 0u;
+      qf[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1p + 2 * d) : 0u;
+      qf[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0p + 2 * (d + 8)) : 0u;
+      qf[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1p + 2 * (d + 8)) : 0u;
+    }
+  }
+
+  float oacc[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};  // log2 domain (already scaled)
+  float l_run[2] = {0.f, 0.f};              // this thread's share of the row sums
+  const float sl2 = a.scale_log2;
+
+  // ldmatrix lane roles
+  const int lm_mi = lane >> 3;
+  const int lm_r = lane & 7;
+
+  for (int i = 0; i < nt_w; ++i) {
+    cp_async_wait<kStages - 2>();
+    __syncwarp();
+    issue_tile(i + kStages - 1);
+
+    const uint32_t sk = wsm_u32 + (i % kStages) * 2 * kTileBytes;
+    const uint32_t sv = sk + kTileBytes;
+    const int key0 = c0 + (warp + i * kWarps) * kTileKeys;
+
+    // ---- S[16 heads x 16 keys] = Q K^T ----
+    float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t r0, r1, r2, r3;
+      const int key = (lm_mi >> 1) * 8 + lm_r;
+      const int chunk = 2 * ks + (lm_mi & 1);
+      ldmatrix_x4(sk + swz<D>(key, chunk), r0, r1, r2, r3);
+      mma_16816<BF16>(sacc[0], qf[ks], r0, r1);
+      mma_16816<BF16>(sacc[1], qf[ks], r2, r3);
+    }
+
+    // ---- scale, mask the ragged end, online softmax ----
+    const bool partial = key0 + kTileKeys > c1;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float s = sacc[nb][e] * sl2;
+        if (partial && (key0 + nb * 8 + tq * 2 + (e & 1) >= c1)) s = -INFINITY;
+        sacc[nb][e] = s;
+      }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float mx = fmaxf(fmaxf(sacc[0][2 * r], sacc[0][2 * r + 1]), fmaxf(sacc[1][2 * r], sacc[1][2 * r + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+      const float m_new = fmaxf(m_run[r], mx);  // finite: every tile holds at least one live key
+      alpha[r] = ex2_approx(m_run[r] - m_new);  // first tile: exp2(-inf) = 0
+      m_run[r] = m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        const float p0 = ex2_approx(sacc[nb][2 * r] - m_new);
+        const float p1 = ex2_approx(sacc[nb][2 * r + 1] - m_new);
+        sacc[nb][2 * r] = p0;
+        sacc[nb][2 * r + 1] = p1;
+        sum += p0 + p1;
+      }
+      l_run[r] = l_run[r] * alpha[r] + sum;
+    }
+    if (__any_sync(0xFFFFFFFFu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) {
+        oacc[n][0] *= alpha[0];
+        oacc[n][1] *= alpha[0];
+        oacc[n][2] *= alpha[1];
+        oacc[n][3] *= alpha[1];
+      }
+    }
+    uint32_t pa[4];
+    pa[0] = pack2<BF16>(sacc[0][0], sacc[0][1]);
+    pa[1] = pack2<BF16>(sacc[0][2], sacc[0][3]);
+    pa[2] = pack2<BF16>(sacc[1][0], sacc[1][1]);
+    pa[3] = pack2<BF16>(sacc[1][2], sacc[1][3]);
+
+    // ---- O[16 heads x D] += P V ----
+#pragma unroll
+    for (int dn = 0; dn < D / 16; ++dn) {
+      uint32_t r0, r1, r2, r3;
+      const int key = (lm_mi & 1) * 8 + lm_r;
+      const int chunk = 2 * dn + (lm_mi >> 1);
+      ldmatrix_x4_trans(sv + swz<D>(key, chunk), r0, r1, r2, r3);
+      mma_16816<BF16>(oacc[2 * dn], pa, r0, r1);
+      mma_16816<BF16>(oacc[2 * dn + 1], pa, r2, r3);
+    }
+  }
+  cp_async_wait<0>();
+
+  // ---- row sums across the 4 lanes of a row ----
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xFFFFFFFFu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xFFFFFFFFu, l_run[r], 2);
+  }
+
+  // ---- merge the warps through shared memory (reusing the ring buffers) ----
+  __syncthreads();
+  float* mo = reinterpret_cast<float*>(wsm);             // [16][D]
+  float* mml = reinterpret_cast<float*>(wsm) + 16 * D;   // [16][2]
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int g = g0 + 8 * r;
+    if (g < a.group) {
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n)
+        *reinterpret_cast<float2*>(&mo[g * D + n * 8 + tq * 2]) = make_float2(oacc[n][2 * r], oacc[n][2 * r + 1]);
+      if (tq == 0) {
+        mml[g * 2] = m_run[r];
+        mml[g * 2 + 1] = l_run[r];
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < a.group * D; idx += kWarps * 32) {
+    const int g = idx / D;
+    const int d = idx % D;
+    float mw[kWarps];
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      mw[w] = reinterpret_cast<const float*>(smem + w * kWarpBytes)[16 * D + g * 2];
+      M = fmaxf(M, mw[w]);
+    }
+    float o = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float* wf = reinterpret_cast<const float*>(smem + w * kWarpBytes);
+      const float sc = (mw[w] == -INFINITY) ? 0.f : ex2_approx(mw[w] - M);
+      o += sc * wf[g * D + d];
+      l += sc * wf[16 * D + g * 2 + 1];
+    }
+    const int h = kvh * a.group + g;
+    const size_t pidx = (static_cast<size_t>(b) * a.n_heads + h) * a.n_split + split;
+    a.part_o[pidx * D + d] = o;
+    if (d == 0) {
+      a.part_ml[pidx * 2] = M;
+      a.part_ml[pidx * 2 + 1] = l;
+    }
+  }
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
+  const int h = blockIdx.x;
+  const int b = blockIdx.y;
+  const int d = threadIdx.x;
+  const int len = min(a.lens[b], a.max_len);
+  const int ns = (len + a.chunk - 1) / a.chunk;
+  const size_t p0 = (static_cast<size_t>(b) * a.n_heads + h) * a.n_split;
+  float M = -INFINITY;
+  for (int s = 0; s < ns; ++s) M = fmaxf(M, a.part_ml[(p0 + s) * 2]);
+  float o = 0.f, l = 0.f;
+  for (int s = 0; s < ns; ++s) {
+    const float sc = ex2_approx(a.part_ml[(p0 + s) * 2] - M);
+    l += sc * a.part_ml[(p0 + s) * 2 + 1];
+    o += sc * a.part_o[(p0 + s) * D + d];
+  }
+  const float r = (l > 0.f) ? o / l : 0.f;
+  uint8_t* op = reinterpret_cast<uint8_t*>(a.out) +
+                2 * (static_cast<size_t>(b) * a.out_stride[0] + static_cast<size_t>(h) * a.out_stride[1] + d);
+  if constexpr (BF16) *reinterpret_cast<__nv_bfloat16*>(op) = __float2bfloat16_rn(r);
+  else *reinterpret_cast<__half*>(op) = __float2half_rn(r);
+}
+
+template <int D, bool BF16>
+cudaError_t launch_one(const DecodeArgs& a, cudaStream_t stream) {
+  constexpr int smem = kWarps * kStages * 2 * kTileKeys * D * 2;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 64 && !attr_done[dev]) {
+    e = cudaFuncSetAttribute(decode_split_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    attr_done[dev] = true;
+  }
+  dim3 grid(a.n_split, a.n_kv_heads, a.batch);
+  decode_split_kernel<D, BF16><<<grid, kWarps * 32, smem, stream>>>(a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  decode_combine_kernel<D, BF16><<<dim3(a.n_heads, a.batch), D, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_decode(const DecodeArgs& a, int head_dim, bool bf16, cudaStream_t stream) {
+  if (head_dim == 128) return bf16 ? launch_one<128, true>(a, stream) : launch_one<128, false>(a, stream);
+  return bf16 ? launch_one<64, true>(a, stream) : launch_one<64, false>(a, stream);
+}
+
+}  // namespace minfer_attn

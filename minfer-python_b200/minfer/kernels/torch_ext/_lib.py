@@ -1,0 +1,105 @@
+"""ctypes binding of libminfer_attn.so (declarations: include/minfer_attn.h).
+
+The library is the only compute path.  If it is missing, importing this
+module raises: there is no CPU or PyTorch fallback behind the ops.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libminfer_attn.so")
+
+F16 = 0
+BF16 = 1
+
+EXPORTS = (
+    "minfer_attn_prefill",
+    "minfer_attn_decode",
+    "minfer_attn_decode_workspace_bytes",
+    "minfer_attn_decode_default_chunk",
+    "minfer_attn_strerror",
+    "minfer_attn_abi_version",
+)
+
+
+class PrefillParams(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p),
+        ("k", ctypes.c_void_p),
+        ("v", ctypes.c_void_p),
+        ("out", ctypes.c_void_p),
+        ("mask", ctypes.c_void_p),
+        ("status", ctypes.c_void_p),
+        ("q_stride", ctypes.c_int64 * 3),
+        ("kv_stride", ctypes.c_int64 * 3),
+        ("out_stride", ctypes.c_int64 * 3),
+        ("batch", ctypes.c_int32),
+        ("n_heads", ctypes.c_int32),
+        ("n_kv_heads", ctypes.c_int32),
+        ("seq_q", ctypes.c_int32),
+        ("seq_k", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("dtype", ctypes.c_int32),
+        ("causal", ctypes.c_int32),
+        ("softmax_scale", ctypes.c_float),
+        ("flags", ctypes.c_int32),
+    ]
+
+
+class DecodeParams(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p),
+        ("k_cache", ctypes.c_void_p),
+        ("v_cache", ctypes.c_void_p),
+        ("lens", ctypes.c_void_p),
+        ("out", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
+        ("q_stride", ctypes.c_int64 * 2),
+        ("kv_stride", ctypes.c_int64 * 3),
+        ("out_stride", ctypes.c_int64 * 2),
+        ("batch", ctypes.c_int32),
+        ("n_heads", ctypes.c_int32),
+        ("n_kv_heads", ctypes.c_int32),
+        ("max_len", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("dtype", ctypes.c_int32),
+        ("chunk", ctypes.c_int32),
+        ("softmax_scale", ctypes.c_float),
+    ]
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python build.py` in the package root "
+            "(nvcc, sm_100a). There is no fallback implementation."
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.minfer_attn_prefill.argtypes = [ctypes.POINTER(PrefillParams), ctypes.c_void_p]
+    lib.minfer_attn_prefill.restype = ctypes.c_int
+    lib.minfer_attn_decode.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
+    lib.minfer_attn_decode.restype = ctypes.c_int
+    lib.minfer_attn_decode_workspace_bytes.argtypes = [ctypes.c_int32] * 5
+    lib.minfer_attn_decode_workspace_bytes.restype = ctypes.c_size_t
+    lib.minfer_attn_decode_default_chunk.argtypes = [ctypes.c_int32] * 3
+    lib.minfer_attn_decode_default_chunk.restype = ctypes.c_int32
+    lib.minfer_attn_strerror.argtypes = [ctypes.c_int]
+    lib.minfer_attn_strerror.restype = ctypes.c_char_p
+    lib.minfer_attn_abi_version.argtypes = []
+    lib.minfer_attn_abi_version.restype = ctypes.c_int
+    return lib
+
+
+lib = _load()
+
+
+def strerror(code: int) -> str:
+    return lib.minfer_attn_strerror(code).decode()
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what}: {strerror(code)} (code {code})")

@@ -1,0 +1,221 @@
+"""Python op surface of the attention path.
+
+`flash_attn` keeps the reference's wrapper signature and schema
+(src/minfer/kernels/torch_ext/ops.py:234-266, csrc/reg.cpp:30 of
+dsuarez01/minfer-python) and the argument checks of its launcher
+(csrc/cuda/flash_attn/op.cuh:32-78), relaxed only to admit bfloat16 and
+head_dim 64.  `flash_attn_causal` and `flash_attn_decode` are additions the
+reference has no counterpart for.  Every op forwards raw pointers, strides
+and the current CUDA stream to libminfer_attn.so; nothing here computes.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+
+_DEBUG = os.environ.get("MINFER_ATTN_DEBUG", "0") not in ("", "0")
+
+_DEFS = {
+    "flash_attn": "(int qtype_int, int qblock_size, int qtype_size, Tensor q, Tensor k, Tensor v, "
+                  "Tensor(a!) mask, Tensor(a!) out) -> ()",
+    "flash_attn_causal": "(Tensor q, Tensor k, Tensor v, Tensor(a!) out) -> ()",
+    "flash_attn_decode": "(Tensor q, Tensor k_cache, Tensor v_cache, Tensor lens, Tensor(a!) out) -> ()",
+}
+_library = torch.library.Library("minfer", "FRAGMENT")
+for _name, _schema in _DEFS.items():
+    _library.define(_name + _schema)
+
+_status: dict[int, torch.Tensor] = {}
+_workspace: dict[int, torch.Tensor] = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=device)
+        _status[idx] = t
+    return t
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if a kernel on `device` gave up a bounded wait."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    t = _status_word(device)
+    torch.cuda.synchronize(device)
+    vals = t.tolist()
+    if vals[0] != 0:
+        t.zero_()
+        raise RuntimeError(f"minfer attention kernel reported status {vals} (code, block x, block y/z, wait site)")
+
+
+def _dtype_tag(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return _lib.F16
+    if t.dtype == torch.bfloat16:
+        return _lib.BF16
+    raise RuntimeError(f"minfer attention: dtype {t.dtype} not supported (float16 or bfloat16)")
+
+
+def _check_qkv(q, k, v, out):
+    torch._check(q.is_cuda and k.is_cuda and v.is_cuda and out.is_cuda, lambda: "all tensors must be on CUDA")
+    torch._check(q.device == k.device == v.device == out.device, lambda: "tensors on different devices")
+    torch._check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and out.dim() == 4, lambda: "tensors must be 4-D")
+    torch._check(q.dtype == k.dtype == v.dtype == out.dtype, lambda: "q, k, v, out must share one dtype")
+    torch._check(q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and out.stride(-1) == 1,
+                 lambda: "innermost stride must be 1")
+    torch._check(k.stride()[:3] == v.stride()[:3], lambda: "k and v must share strides")
+    torch._check(q.shape == out.shape, lambda: "q and out shapes differ")
+    torch._check(k.shape == v.shape, lambda: "k and v shapes differ")
+    torch._check(q.size(0) == k.size(0) and q.size(3) == k.size(3), lambda: "batch or head_dim mismatch")
+    torch._check(q.size(1) % k.size(1) == 0, lambda: "n_heads must be a multiple of n_kv_heads")
+
+
+def _prefill(q, k, v, mask, out, causal: bool) -> None:
+    p = _lib.PrefillParams()
+    p.q, p.k, p.v, p.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    p.mask = mask.data_ptr() if mask is not None else None
+    p.status = _status_word(q.device).data_ptr()
+    for i in range(3):
+        p.q_stride[i] = q.stride(i)
+        p.kv_stride[i] = k.stride(i)
+        p.out_stride[i] = out.stride(i)
+    p.batch, p.n_heads, p.n_kv_heads = q.size(0), q.size(1), k.size(1)
+    p.seq_q, p.seq_k, p.head_dim = q.size(2), k.size(2), q.size(3)
+    p.dtype = _dtype_tag(q)
+    p.causal = 1 if causal else 0
+    p.softmax_scale = 0.0
+    p.flags = 0
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib.lib.minfer_attn_prefill(ctypes.byref(p), ctypes.c_void_p(stream)), "minfer_attn_prefill")
+    if _DEBUG:
+        check_status(q.device)
+
+
+def _flash_attn_cuda(qtype_int, qblock_size, qtype_size, q, k, v, mask, out) -> None:
+    _check_qkv(q, k, v, out)
+    torch._check(mask.is_cuda and mask.device == q.device, lambda: "mask must be on the same CUDA device")
+    torch._check(mask.dtype == torch.bool, lambda: "mask must be bool")
+    torch._check(mask.dim() == 4 and mask.is_contiguous(), lambda: "mask must be a contiguous 4-D tensor")
+    torch._check(q.size(2) == k.size(2), lambda: "flash_attn requires seq_q == seq_k")
+    torch._check(tuple(mask.shape) == (q.size(0), 1, q.size(2), k.size(2)), lambda: "mask must be [B, 1, L, L]")
+    _prefill(q, k, v, mask, out, causal=False)
+
+
+def _flash_attn_causal_cuda(q, k, v, out) -> None:
+    _check_qkv(q, k, v, out)
+    torch._check(k.size(2) >= q.size(2), lambda: "causal attention requires seq_k >= seq_q")
+    _prefill(q, k, v, None, out, causal=True)
+
+
+def _decode_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _workspace.get(idx)
+    if t is None or t.numel() < nbytes:
+        t = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspace[idx] = t
+    return t
+
+
+def _flash_attn_decode_cuda(q, k_cache, v_cache, lens, out) -> None:
+    _check_qkv(q, k_cache, v_cache, out)
+    torch._check(q.size(2) == 1, lambda: "decode takes one query token per sequence")
+    torch._check(lens.is_cuda and lens.device == q.device, lambda: "lens must be on the same CUDA device")
+    torch._check(lens.dtype == torch.int32 and lens.dim() == 1 and lens.is_contiguous(),
+                 lambda: "lens must be a contiguous int32 vector")
+    torch._check(lens.numel() == q.size(0), lambda: "lens must have one entry per sequence")
+    p = _lib.DecodeParams()
+    p.q, p.k_cache, p.v_cache = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
+    p.lens, p.out = lens.data_ptr(), out.data_ptr()
+    p.batch, p.n_heads, p.n_kv_heads = q.size(0), q.size(1), k_cache.size(1)
+    p.max_len, p.head_dim = k_cache.size(2), q.size(3)
+    p.dtype = _dtype_tag(q)
+    p.chunk = 0
+    p.softmax_scale = 0.0
+    for i in range(2):
+        p.q_stride[i] = q.stride(i)
+        p.out_stride[i] = out.stride(i)
+    for i in range(3):
+        p.kv_stride[i] = k_cache.stride(i)
+    need = _lib.lib.minfer_attn_decode_workspace_bytes(p.batch, p.n_heads, p.max_len, p.head_dim, 0)
+    ws = _decode_workspace(q.device, need)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib.lib.minfer_attn_decode(ctypes.byref(p), ctypes.c_void_p(stream)), "minfer_attn_decode")
+
+
+_library.impl("flash_attn", _flash_attn_cuda, "CUDA")
+_library.impl("flash_attn_causal", _flash_attn_causal_cuda, "CUDA")
+_library.impl("flash_attn_decode", _flash_attn_decode_cuda, "CUDA")
+
+
+def flash_attn(
+    qtype_int: int,
+    qblock_size: int,
+    qtype_size: int,
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    mask: torch.Tensor,
+    out: torch.Tensor,
+):
+    """
+    attention with a dense bool mask [B, 1, L, L] (True = attend); result written to `out`.
+    q/out: [B, n_heads, L, D], k/v: [B, n_kv_heads, L, D]; the three leading ints are unused
+    by attention, as in the reference.
+    """
+    return torch.ops.minfer.flash_attn.default(qtype_int, qblock_size, qtype_size, q, k, v, mask, out)
+
+
+def flash_attn_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor):
+    """causal attention (key j visible to query i iff j <= i + Lk - Lq) without a materialised mask."""
+    return torch.ops.minfer.flash_attn_causal.default(q, k, v, out)
+
+
+def flash_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, lens: torch.Tensor,
+                      out: torch.Tensor):
+    """
+    one-token decode over a padded KV cache: q/out [B, n_heads, 1, D], caches
+    [B, n_kv_heads, max_len, D], lens int32 [B]; sequence b attends keys [0, lens[b]).
+    """
+    return torch.ops.minfer.flash_attn_decode.default(q, k_cache, v_cache, lens, out)
+
+
+@torch.library.register_fake("minfer::flash_attn")
+def _(qtype_int, qblock_size, qtype_size, q, k, v, mask, out):
+    torch._check(q.dtype in (torch.float16, torch.bfloat16))
+    torch._check(k.dtype == q.dtype)
+    torch._check(v.dtype == q.dtype)
+    torch._check(mask.dtype == torch.bool)
+    torch._check(out.dtype == q.dtype)
+    torch._check(q.device == k.device == v.device == out.device)
+    torch._check(q.device.type == "cuda")
+    torch._check(q.dim() == 4)
+    torch._check(k.dim() == 4)
+    torch._check(v.dim() == 4)
+    torch._check(mask.dim() == 4)
+    torch._check(out.dim() == 4)
+
+
+@torch.library.register_fake("minfer::flash_attn_causal")
+def _(q, k, v, out):
+    torch._check(q.dtype in (torch.float16, torch.bfloat16))
+    torch._check(k.dtype == q.dtype and v.dtype == q.dtype and out.dtype == q.dtype)
+    torch._check(q.device.type == "cuda")
+    torch._check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and out.dim() == 4)
+
+
+@torch.library.register_fake("minfer::flash_attn_decode")
+def _(q, k_cache, v_cache, lens, out):
+    torch._check(q.dtype in (torch.float16, torch.bfloat16))
+    torch._check(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype == q.dtype)
+    torch._check(lens.dtype == torch.int32)
+    torch._check(q.device.type == "cuda")
+    torch._check(q.dim() == 4 and k_cache.dim() == 4 and v_cache.dim() == 4 and out.dim() == 4)
+    torch._check(lens.dim() == 1)

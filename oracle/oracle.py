@@ -1,0 +1,146 @@
+"""CPU oracle for the attention path — TEST INFRASTRUCTURE ONLY.
+
+Only tests/, the smoke check and the benchmark's CPU-baseline leg import this
+module; the product library never does.
+
+Two restatements of the reference's semantics live here:
+
+* `sdpa_reference(Q, K, V, mask)` — the reference's own CPU path restated: its
+  refs.flash_attn is one call to torch's scaled_dot_product_attention with
+  attn_mask (src/minfer/kernels/refs.py:53-55 of dsuarez01/minfer-python), and
+  its callers expand K/V for grouped-query heads with repeat_interleave
+  (test/kernels.py:253-255, apps/benchmark.py:240-242).  The arithmetic is
+  PyTorch ATen's (torch 2.10.0 pinned by the reference, uv.lock:601-602).
+* `attention_f64(...)` — the definition out = softmax(q k^T * scale + mask) v
+  written out in C with double accumulation (attn_oracle.c), independent of
+  torch; used to cross-check the first and to check row blocks of problems too
+  large for a dense SDPA call.
+
+Pinned: tests/golden/ holds outputs of the reference's refs.flash_attn itself
+(imported from the reference tree by tests/golden/make_golden.py); the CPU test
+suite checks both restatements against those vectors.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "_build", "libattn_oracle.so")
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    """Compile attn_oracle.c (gcc) if the shared object is missing or stale."""
+    src = os.path.join(_HERE, "attn_oracle.c")
+    if force or not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(src):
+        os.makedirs(os.path.dirname(_LIB), exist_ok=True)
+        cc = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else "gcc"
+        base = [cc, "-O2", "-fPIC", "-shared", "-o", _LIB, src, "-lm"]
+        if subprocess.run(base[:3] + ["-fopenmp"] + base[3:], capture_output=True).returncode != 0:
+            subprocess.run(base, check=True)
+    return _LIB
+
+
+def _load():
+    global _lib
+    if _lib is None:
+        build()
+        lib = ctypes.CDLL(_LIB)
+        lib.attn_oracle_f32.restype = ctypes.c_int
+        lib.attn_oracle_f32.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 6 + [ctypes.c_float] + [ctypes.c_int] * 3
+        _lib = lib
+    return _lib
+
+
+def attention_f64(q, k, v, mask=None, lens=None, causal=False, scale=0.0, rows=None) -> torch.Tensor:
+    """softmax(q k^T * scale + mask) v with double accumulation, on CPU.
+
+    q [B,H,Lq,D], k/v [B,Hkv,Lk,D] (any float dtype; upcast to fp32 exactly),
+    mask bool [B,1,Lq,Lk] or None, lens int [B] or None, causal j <= i + Lk - Lq.
+    rows=(r0, r1) restricts the computed query rows; the returned fp32 tensor has
+    only those rows.
+    """
+    lib = _load()
+    q32 = q.detach().to("cpu", torch.float32).contiguous()
+    k32 = k.detach().to("cpu", torch.float32).contiguous()
+    v32 = v.detach().to("cpu", torch.float32).contiguous()
+    B, H, Lq, D = q32.shape
+    Hkv, Lk = k32.shape[1], k32.shape[2]
+    r0, r1 = (0, Lq) if rows is None else rows
+    out = torch.zeros_like(q32)
+    m8 = None
+    if mask is not None:
+        m8 = mask.detach().to("cpu").expand(B, 1, Lq, Lk).to(torch.uint8).contiguous()
+    l32 = None
+    if lens is not None:
+        l32 = lens.detach().to("cpu", torch.int32).contiguous()
+    rc = lib.attn_oracle_f32(
+        q32.data_ptr(), k32.data_ptr(), v32.data_ptr(),
+        m8.data_ptr() if m8 is not None else None,
+        l32.data_ptr() if l32 is not None else None,
+        out.data_ptr(), B, H, Hkv, Lq, Lk, D, float(scale), int(bool(causal)), int(r0), int(r1))
+    if rc != 0:
+        raise RuntimeError(f"attn_oracle_f32 failed with {rc}")
+    return out[:, :, r0:r1, :]
+
+
+def expand_kv(x: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """Grouped-query expansion exactly as the reference's callers do it."""
+    n_rep = n_heads // x.shape[1]
+    return x if n_rep == 1 else x.repeat_interleave(n_rep, dim=1)
+
+
+def sdpa_reference(Q, K, V, mask) -> torch.Tensor:
+    """The reference's refs.flash_attn restated; K/V must already be expanded."""
+    return F.scaled_dot_product_attention(Q, K, V, attn_mask=mask)
+
+
+def causal_mask(B: int, L: int) -> torch.Tensor:
+    """The reference's causal mask construction (test/kernels.py:242)."""
+    return (torch.arange(L).unsqueeze(0) <= torch.arange(L).unsqueeze(1)).unsqueeze(0).unsqueeze(0).expand(B, 1, L, L).to(torch.bool)
+
+
+def window_mask(B: int, L: int, window: int) -> torch.Tensor:
+    """The reference's symmetric sliding-window mask (test/kernels.py:276-278)."""
+    dist = torch.arange(L).unsqueeze(0) - torch.arange(L).unsqueeze(1)
+    return (dist.abs() < window).unsqueeze(0).unsqueeze(0).expand(B, 1, L, L).to(torch.bool)
+
+
+def length_mask(lens: torch.Tensor, max_len: int) -> torch.Tensor:
+    """Decode mask: sequence b sees keys [0, lens[b]).  Shape [B,1,1,max_len]."""
+    return (torch.arange(max_len)[None, :] < lens.to(torch.int64)[:, None])[:, None, None, :]
+
+
+def prefill_oracle(q, k, v, mask=None, causal=False) -> torch.Tensor:
+    """fp32 oracle for prefill: inputs upcast to fp32, reference SDPA path."""
+    B, H, L, _ = q.shape
+    qf, kf, vf = q.float().cpu(), k.float().cpu(), v.float().cpu()
+    if causal and mask is None:
+        mask = causal_mask(B, L) if k.shape[2] == L else None
+        if mask is None:
+            return attention_f64(qf, kf, vf, causal=True)
+    return sdpa_reference(qf, expand_kv(kf, H), expand_kv(vf, H), mask.cpu() if mask is not None else None)
+
+
+def decode_oracle(q, k_cache, v_cache, lens) -> torch.Tensor:
+    """fp32 oracle for decode: reference SDPA path with the length mask."""
+    H = q.shape[1]
+    qf, kf, vf = q.float().cpu(), k_cache.float().cpu(), v_cache.float().cpu()
+    m = length_mask(lens.cpu(), k_cache.shape[2])
+    return F.scaled_dot_product_attention(qf, kf, vf, attn_mask=m, enable_gqa=(kf.shape[1] != H))
+
+
+def within_tolerance(actual: torch.Tensor, expected: torch.Tensor, atol: float = 2e-3, rtol: float = 2e-3):
+    """allclose with the path's stated tolerance; returns (ok, max_abs_err, n_bad)."""
+    a = actual.detach().float().cpu()
+    e = expected.detach().float().cpu()
+    err = (a - e).abs()
+    bad = err > (atol + rtol * e.abs())
+    bad |= ~torch.isfinite(a)
+    return (not bool(bad.any())), float(err.max()), int(bad.sum())

@@ -1,0 +1,68 @@
+"""Shared helpers for the test-suite: golden-vector loading and seeded inputs."""
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import torch
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+# tolerance the attention path states for 16-bit outputs against the fp32 oracle
+ATOL = 2e-3
+RTOL = 2e-3
+
+
+def from_bits16(a: np.ndarray, bf16: bool) -> torch.Tensor:
+    t = torch.from_numpy(a.view(np.int16).copy())
+    return t.view(torch.bfloat16 if bf16 else torch.float16)
+
+
+def load_prefill(name: str):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    bf16 = bool(z["bf16"])
+    shape = tuple(int(x) for x in z["mask_shape"])
+    n = int(np.prod(shape))
+    mask = torch.from_numpy(np.unpackbits(z["mask"])[:n].astype(bool).reshape(shape))
+    return (from_bits16(z["q"], bf16), from_bits16(z["k"], bf16), from_bits16(z["v"], bf16), mask,
+            torch.from_numpy(z["out"]))
+
+
+def load_decode(name: str):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    bf16 = bool(z["bf16"])
+    return (from_bits16(z["q"], bf16), from_bits16(z["k"], bf16), from_bits16(z["v"], bf16),
+            torch.from_numpy(z["lens"]), torch.from_numpy(z["out"]))
+
+
+def seeded_qkv(seed, B, H, Hkv, Lq, Lk, D, dtype):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, H, Lq, D, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, Lk, D, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, Lk, D, generator=g).to(dtype)
+    return q, k, v
+
+
+def bf16_half_ulp(x: torch.Tensor) -> torch.Tensor:
+    """Half a bfloat16 ulp at |x| (8 significand bits): rounding the exact result to
+    bfloat16 already moves it by up to this much."""
+    ax = x.abs().float().clamp_min(2.0 ** -126)
+    return torch.exp2(torch.floor(torch.log2(ax)) - 8)
+
+
+def check_close(actual: torch.Tensor, expected: torch.Tensor, what: str = "", bf16: bool = False):
+    """The path's tolerance: atol = rtol = 2e-3 against the fp32 oracle.  For bfloat16
+    outputs the representation error of the output type itself (half an ulp) is added,
+    since rounding the exact value to bfloat16 can exceed 2e-3 for |x| >= 2."""
+    a = actual.detach().float().cpu()
+    e = expected.detach().float().cpu()
+    assert a.shape == e.shape, f"{what}: shape {tuple(a.shape)} vs {tuple(e.shape)}"
+    assert torch.isfinite(a).all(), f"{what}: non-finite values in the result"
+    tol = ATOL + RTOL * e.abs()
+    if bf16:
+        tol = tol + bf16_half_ulp(e)
+    err = (a - e).abs()
+    bad = err > tol
+    assert not bad.any(), (f"{what}: {int(bad.sum())} of {bad.numel()} elements out of tolerance, "
+                           f"max abs err {float(err.max()):.3e}")
+    return float(err.max())

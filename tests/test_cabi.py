@@ -1,0 +1,89 @@
+"""CPU: the C-ABI library loads, exports what include/minfer_attn.h declares, and
+rejects bad arguments before touching a device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "minfer_attn.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(minfer_attn_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_entry_points():
+    syms = declared_symbols()
+    for s in ("minfer_attn_prefill", "minfer_attn_decode", "minfer_attn_decode_workspace_bytes",
+              "minfer_attn_strerror", "minfer_attn_abi_version"):
+        assert s in syms
+
+
+def test_library_exports_every_declared_symbol():
+    from minfer.kernels.torch_ext import _lib
+    for s in declared_symbols():
+        assert hasattr(_lib.lib, s), f"{s} declared in the header but not exported"
+    assert _lib.lib.minfer_attn_abi_version() == 1
+    assert set(_lib.EXPORTS) <= set(declared_symbols())
+
+
+def test_invalid_arguments_are_rejected_without_a_device():
+    from minfer.kernels.torch_ext import _lib
+    L = _lib.lib
+    assert L.minfer_attn_prefill(None, None) == 1
+    p = _lib.PrefillParams()
+    assert L.minfer_attn_prefill(ctypes.byref(p), None) == 1          # null pointers
+    p.q = p.k = p.v = p.out = 0x1000
+    p.batch, p.n_heads, p.n_kv_heads, p.seq_q, p.seq_k, p.head_dim = 1, 6, 4, 128, 128, 128
+    assert L.minfer_attn_prefill(ctypes.byref(p), None) == 1          # heads not a multiple of kv heads
+    p.n_kv_heads = 2
+    p.head_dim = 96
+    assert L.minfer_attn_prefill(ctypes.byref(p), None) == 2          # unsupported head_dim
+    p.head_dim = 128
+    p.q = 0x1004
+    assert L.minfer_attn_prefill(ctypes.byref(p), None) == 1          # misaligned base pointer
+    p.q = 0x1000
+    p.q_stride[2] = 132
+    assert L.minfer_attn_prefill(ctypes.byref(p), None) == 1          # stride not a multiple of 8 elements
+    p.q_stride[2] = 128
+    p.causal, p.seq_k = 1, 64
+    assert L.minfer_attn_prefill(ctypes.byref(p), None) == 1          # causal with fewer keys than queries
+    d = _lib.DecodeParams()
+    assert L.minfer_attn_decode(ctypes.byref(d), None) == 1
+    d.q = d.k_cache = d.v_cache = d.lens = d.out = 0x1000
+    d.batch, d.n_heads, d.n_kv_heads, d.max_len, d.head_dim = 2, 8, 2, 1024, 128
+    d.chunk = 100
+    assert L.minfer_attn_decode(ctypes.byref(d), None) == 1           # chunk not a multiple of 64
+    d.chunk = 0
+    assert L.minfer_attn_decode(ctypes.byref(d), None) == 5           # no workspace
+    d.n_heads, d.n_kv_heads = 34, 2
+    assert L.minfer_attn_decode(ctypes.byref(d), None) == 2           # group of 17 > 16
+    for code in range(0, 6):
+        assert len(_lib.strerror(code)) > 0
+
+
+def test_workspace_size_formula():
+    from minfer.kernels.torch_ext import _lib
+    L = _lib.lib
+    assert L.minfer_attn_decode_default_chunk(64, 8, 8192) == 512
+    assert L.minfer_attn_decode_workspace_bytes(64, 32, 8192, 128, 512) == 64 * 32 * 16 * 130 * 4
+    assert L.minfer_attn_decode_workspace_bytes(64, 32, 8192, 128, 0) == 64 * 32 * 16 * 130 * 4
+    assert L.minfer_attn_decode_workspace_bytes(64, 32, 8192, 96, 512) == 0
+    assert L.minfer_attn_decode_workspace_bytes(1, 1, 1, 64, 64) == 66 * 4
+
+
+def test_ops_have_no_cpu_path():
+    import torch
+    from minfer.kernels import KernelBackend
+    k = KernelBackend("torch_ext")
+    q = torch.zeros(1, 2, 8, 64, dtype=torch.float16)
+    m = torch.ones(1, 1, 8, 8, dtype=torch.bool)
+    with pytest.raises(NotImplementedError):
+        k.flash_attn(1, 1, 2, q, q, q, m, q.clone())
+    with pytest.raises(NotImplementedError):
+        k.flash_attn_causal(q, q, q, q.clone())
+    with pytest.raises(ValueError):
+        KernelBackend("triton")

@@ -1,0 +1,181 @@
+"""GPU parity tests of the prefill path, through the op surface and the C ABI.
+
+Tolerance: atol = rtol = 2e-3 against the fp32 oracle (see _util.check_close)."""
+import pytest
+import torch
+
+from _util import check_close, load_prefill, seeded_qkv
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+F16 = (1, 1, 2)  # qtype F16, qblock_size, qtype_size: what the reference's callers pass
+
+
+def run_masked(kerns, q, k, v, mask):
+    out = torch.full(q.shape, float("nan"), dtype=q.dtype, device="cuda")
+    kerns.flash_attn(*F16, q.cuda(), k.cuda(), v.cuda(), mask.cuda(), out)
+    from minfer.kernels.torch_ext.ops import check_status
+    check_status()
+    return out
+
+
+def run_causal(kerns, q, k, v):
+    out = torch.full(q.shape, float("nan"), dtype=q.dtype, device="cuda")
+    kerns.flash_attn_causal(q.cuda(), k.cuda(), v.cuda(), out)
+    from minfer.kernels.torch_ext.ops import check_status
+    check_status()
+    return out
+
+
+@pytest.mark.parametrize("name", ["prefill_causal_g4_d128", "prefill_window_g6_d128", "prefill_random_g1_d64",
+                                  "prefill_causal_bf16_g8_d128", "prefill_causal_g4_d64"])
+def test_golden_vectors_dense_mask(kerns, name):
+    q, k, v, mask, want = load_prefill(name)
+    got = run_masked(kerns, q, k, v, mask)
+    check_close(got, want, name, bf16=q.dtype == torch.bfloat16)
+
+
+@pytest.mark.parametrize("name", ["prefill_causal_g4_d128", "prefill_causal_bf16_g8_d128", "prefill_causal_g4_d64"])
+def test_golden_vectors_causal_fast_path(kerns, name):
+    q, k, v, mask, want = load_prefill(name)
+    got = run_causal(kerns, q, k, v)
+    check_close(got, want, name, bf16=q.dtype == torch.bfloat16)
+
+
+def test_config1_shape_fp16_cast(kerns):
+    """The fp32 CPU self-check configuration, run on the GPU on a float16 cast of its inputs."""
+    q, k, v = seeded_qkv(0, 1, 8, 8, 256, 256, 64, torch.float16)
+    want = O.prefill_oracle(q, k, v, causal=True)
+    check_close(run_causal(kerns, q, k, v), want, "config1")
+
+
+@pytest.mark.parametrize("L", [1, 5, 127, 128, 129, 383, 640])
+@pytest.mark.parametrize("D,H,Hkv", [(128, 4, 1), (64, 6, 1), (128, 3, 3)])
+def test_ragged_lengths_causal_and_mask_agree(kerns, L, D, H, Hkv):
+    q, k, v = seeded_qkv(100 + L, 2, H, Hkv, L, L, D, torch.float16)
+    want = O.prefill_oracle(q, k, v, causal=True)
+    got_c = run_causal(kerns, q, k, v)
+    got_m = run_masked(kerns, q, k, v, O.causal_mask(2, L))
+    check_close(got_c, want, f"causal L={L}")
+    check_close(got_m, want, f"masked L={L}")
+    assert torch.equal(got_c, got_m), "the causal fast path and the dense causal mask must agree bit for bit"
+
+
+def test_bf16_medium(kerns):
+    q, k, v = seeded_qkv(7, 1, 8, 1, 1024, 1024, 128, torch.bfloat16)
+    want = O.prefill_oracle(q, k, v, causal=True)
+    check_close(run_causal(kerns, q, k, v), want, "bf16", bf16=True)
+
+
+def test_strided_views_as_the_reference_callers_pass(kerns):
+    """[B, L, H*D] storage viewed as [B, H, L, D] (test/kernels.py:230-237 of the reference)."""
+    B, L, H, Hkv, D = 2, 512, 12, 2, 128
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(B, L, H * D, generator=g).half().view(B, L, H, D).transpose(1, 2)
+    k = torch.randn(B, L, Hkv * D, generator=g).half().view(B, L, Hkv, D).transpose(1, 2)
+    v = torch.randn(B, L, Hkv * D, generator=g).half().view(B, L, Hkv, D).transpose(1, 2)
+    assert not q.is_contiguous()
+    want = O.prefill_oracle(q, k, v, causal=True)
+    out = torch.zeros(B, H, L, D, dtype=torch.float16, device="cuda")
+    kerns.flash_attn(*F16, q.cuda(), k.cuda(), v.cuda(), O.causal_mask(B, L).cuda(), out)
+    check_close(out, want, "strided")
+    # strided output too
+    out2 = torch.zeros(B, L, H * D, dtype=torch.float16, device="cuda").view(B, L, H, D).transpose(1, 2)
+    kerns.flash_attn_causal(q.cuda(), k.cuda(), v.cuda(), out2)
+    check_close(out2, want, "strided out")
+
+
+def test_head_slices_for_kv_group_sharding(kerns):
+    """A shard of heads (a strided slice) gives the same rows as the full call."""
+    q, k, v = seeded_qkv(9, 1, 16, 4, 384, 384, 128, torch.float16)
+    full = run_causal(kerns, q, k, v)
+    qs, ks, vs = q.cuda()[:, 8:12], k.cuda()[:, 2:3], v.cuda()[:, 2:3]
+    part = torch.zeros(1, 4, 384, 128, dtype=torch.float16, device="cuda")
+    kerns.flash_attn_causal(qs, ks, vs, part)
+    assert torch.equal(part, full[:, 8:12])
+
+
+def test_reference_test_flash_attn_shapes(kerns):
+    """Port of the reference's test_flash_attn (test/kernels.py:222-298): B=8 L=4096 48/8 heads
+    D=128, causal then sliding window 256, inputs as transposed views, K/V scaled by 1/sqrt(D).
+    Checked at the path's own tolerance against the fp32 oracle on sampled row blocks, and at
+    the reference's atol=3e-1 against GPU float16 SDPA on everything."""
+    import torch.nn.functional as F
+    B, L, H, Hkv, D = 8, 4096, 48, 8, 128
+    g = torch.Generator().manual_seed(1234)
+    q = torch.randn(B, L, H * D, generator=g).half().cuda().view(B, L, H, D).transpose(1, 2)
+    k = ((1 / D ** 0.5) * torch.randn(B, L, Hkv * D, generator=g)).half().cuda().view(B, L, Hkv, D).transpose(1, 2)
+    v = ((1 / D ** 0.5) * torch.randn(B, L, Hkv * D, generator=g)).half().cuda().view(B, L, Hkv, D).transpose(1, 2)
+    for kind in ("causal", "window"):
+        mask = (O.causal_mask(B, L) if kind == "causal" else O.window_mask(B, L, 256)).cuda()
+        out = torch.zeros(B, H, L, D, dtype=torch.float16, device="cuda")
+        kerns.flash_attn(*F16, q, k, v, mask, out)
+        torch.cuda.synchronize()
+        expected = F.scaled_dot_product_attention(q, k.repeat_interleave(H // Hkv, dim=1),
+                                                  v.repeat_interleave(H // Hkv, dim=1), attn_mask=mask)
+        assert torch.allclose(expected.cpu(), out.cpu(), atol=3e-1), "flash_attn"
+        del expected
+        for b, rows in ((0, (0, 64)), (3, (2000, 2032)), (7, (4064, 4096))):
+            want = O.attention_f64(q[b:b + 1].cpu(), k[b:b + 1].cpu(), v[b:b + 1].cpu(), mask=mask[b:b + 1].cpu(), rows=rows)
+            check_close(out[b:b + 1, :, rows[0]:rows[1]], want, f"{kind} b={b} rows={rows}")
+        del mask, out
+        torch.cuda.empty_cache()
+
+
+def test_config2_full_size_properties(kerns):
+    """Llama-3-8B-shaped prefill at full size: sampled row blocks against the oracle, plus
+    size-independent properties: row 0 reproduces V's first row, a permutation of the batch
+    permutes the output, and the run is bitwise repeatable."""
+    B, H, Hkv, L, D = 4, 32, 8, 4096, 128
+    q, k, v = seeded_qkv(1, B, H, Hkv, L, L, D, torch.float16)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    out = torch.full((B, H, L, D), float("nan"), dtype=torch.float16, device="cuda")
+    kerns.flash_attn_causal(qc, kc, vc, out)
+    from minfer.kernels.torch_ext.ops import check_status
+    check_status()
+    assert torch.isfinite(out).all()
+    for b, rows in ((0, (0, 40)), (1, (1000, 1024)), (2, (2040, 2060)), (3, (4080, 4096))):
+        want = O.attention_f64(q[b:b + 1], k[b:b + 1], v[b:b + 1], causal=True, rows=rows)
+        check_close(out[b:b + 1, :, rows[0]:rows[1]], want, f"config2 b={b} rows={rows}")
+    # the first token attends only itself
+    assert torch.equal(out[:, :, 0, :], vc[:, :, 0, :].repeat_interleave(H // Hkv, dim=1))
+    perm = torch.tensor([2, 0, 3, 1], device="cuda")
+    out_p = torch.empty_like(out)
+    kerns.flash_attn_causal(qc[perm].contiguous(), kc[perm].contiguous(), vc[perm].contiguous(), out_p)
+    assert torch.equal(out_p, out[perm])
+    out_r = torch.empty_like(out)
+    kerns.flash_attn_causal(qc, kc, vc, out_r)
+    assert torch.equal(out_r, out)
+
+
+def test_argument_errors_raise(kerns):
+    q = torch.zeros(1, 4, 128, 128, dtype=torch.float16, device="cuda")
+    k = torch.zeros(1, 2, 128, 128, dtype=torch.float16, device="cuda")
+    m = torch.ones(1, 1, 128, 128, dtype=torch.bool, device="cuda")
+    out = torch.zeros_like(q)
+    with pytest.raises(RuntimeError):
+        kerns.flash_attn(*F16, q.float(), k.float(), k.float(), m, out.float())      # dtype
+    with pytest.raises(RuntimeError):
+        kerns.flash_attn(*F16, q, k, k[:, :, :64], m, out)                            # k/v shapes differ
+    with pytest.raises(RuntimeError):
+        kerns.flash_attn(*F16, q, k, k, m[..., :64], out)                             # mask shape
+    with pytest.raises(RuntimeError):
+        kerns.flash_attn(*F16, q, k, k, m.to(torch.uint8), out)                       # mask dtype
+    q96 = torch.zeros(1, 4, 128, 96, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError):
+        kerns.flash_attn_causal(q96, q96, q96, torch.zeros_like(q96))                 # head_dim
+    with pytest.raises(RuntimeError):
+        kerns.flash_attn_causal(q, k[:, :, :64], k[:, :, :64], out)                   # fewer keys than queries
+
+
+def test_opcheck(kerns):
+    """torch.library.opcheck on the ops (the reference does this for gemm only, test/kernels.py:167-170)."""
+    q, k, v = seeded_qkv(3, 1, 4, 2, 128, 128, 64, torch.float16)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    out = torch.zeros_like(q)
+    mask = O.causal_mask(1, 128).cuda()
+    torch.library.opcheck(torch.ops.minfer.flash_attn.default, (1, 1, 2, q, k, v, mask, out),
+                          test_utils=("test_schema", "test_faketensor"))
+    torch.library.opcheck(torch.ops.minfer.flash_attn_causal.default, (q, k, v, out),
+                          test_utils=("test_schema", "test_faketensor"))
