@@ -42,6 +42,7 @@ extern "C" {
 #define MINFER_ATTN_ECUDA         3  /* a CUDA runtime / driver call failed          */
 #define MINFER_ATTN_ENODEVICE     4  /* current device is not compute capability 10 */
 #define MINFER_ATTN_EWORKSPACE    5  /* workspace missing or too small              */
+#define MINFER_ATTN_ETOOLARGE     6  /* needs more scratch than the built-in buffer  */
 
 /*
  * Prefill attention:  out = softmax(q k^T * scale + mask) v  with grouped-query
@@ -142,6 +143,30 @@ size_t minfer_attn_decode_workspace_bytes(int32_t batch, int32_t n_heads,
 /* The chunk minfer_attn_decode() uses when params->chunk == 0. */
 int32_t minfer_attn_decode_default_chunk(int32_t batch, int32_t n_kv_heads,
                                          int32_t max_len);
+
+/*
+ * Decode attention without any device allocation, for callers that cannot
+ * allocate: a process that gave all device memory to its own pool at start-up,
+ * or a decode loop that must never reach the allocator.  Same arguments and
+ * results as minfer_attn_decode(), except that params->workspace and
+ * params->workspace_bytes are ignored: the split-KV partials live in a fixed
+ * MINFER_ATTN_STATIC_SCRATCH_BYTES array inside the library (each device that
+ * loads the library holds that much memory until the process exits).
+ *   - A shape whose partials need more than that is refused with
+ *     MINFER_ATTN_ETOOLARGE and nothing is launched (the need is
+ *     minfer_attn_decode_workspace_bytes() for the same arguments).
+ *   - The first call on a device looks up the array's device address; make
+ *     that first call before any stream capture begins on that device.
+ *   - All calls on a device share the one array.  Nothing in it has to start
+ *     at zero (every partial that is read was written earlier in the same
+ *     call), but two calls whose kernels overlap on the GPU race on it: issue
+ *     them on one stream, or order them with events.
+ *   - The function calls neither cudaMalloc/cudaFree nor any allocating
+ *     library routine.
+ * This entry point has no counterpart in the reference.
+ */
+#define MINFER_ATTN_STATIC_SCRATCH_BYTES (32u << 20)
+int minfer_attn_decode_static(const MinferAttnDecodeParams* params, void* stream);
 
 const char* minfer_attn_strerror(int code);
 int minfer_attn_abi_version(void);

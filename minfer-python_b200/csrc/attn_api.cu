@@ -109,6 +109,7 @@ const char* minfer_attn_strerror(int code) {
     case MINFER_ATTN_ECUDA: return "a CUDA runtime or driver call failed";
     case MINFER_ATTN_ENODEVICE: return "current CUDA device is not compute capability 10.x (sm_100)";
     case MINFER_ATTN_EWORKSPACE: return "decode workspace missing or too small";
+    case MINFER_ATTN_ETOOLARGE: return "shape needs more scratch than the library's built-in static buffer holds";
     default: return "unknown error code";
   }
 }

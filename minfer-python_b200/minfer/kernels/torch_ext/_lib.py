@@ -17,6 +17,7 @@ BF16 = 1
 EXPORTS = (
     "minfer_attn_prefill",
     "minfer_attn_decode",
+    "minfer_attn_decode_static",
     "minfer_attn_decode_workspace_bytes",
     "minfer_attn_decode_default_chunk",
     "minfer_attn_strerror",
@@ -82,6 +83,8 @@ def _load() -> ctypes.CDLL:
     lib.minfer_attn_prefill.restype = ctypes.c_int
     lib.minfer_attn_decode.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
     lib.minfer_attn_decode.restype = ctypes.c_int
+    lib.minfer_attn_decode_static.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
+    lib.minfer_attn_decode_static.restype = ctypes.c_int
     lib.minfer_attn_decode_workspace_bytes.argtypes = [ctypes.c_int32] * 5
     lib.minfer_attn_decode_workspace_bytes.restype = ctypes.c_size_t
     lib.minfer_attn_decode_default_chunk.argtypes = [ctypes.c_int32] * 3
