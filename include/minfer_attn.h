@@ -35,6 +35,12 @@ extern "C" {
 #define MINFER_ATTN_F16  0
 #define MINFER_ATTN_BF16 1
 
+/* MinferAttnPrefillParams.flags: run the single-tile kernel (one 128-row query
+ * tile per thread block, no overlap of softmax and MMA) instead of the
+ * two-tile warp-specialised one.  Same results within tolerance; kept for
+ * cross-checking. */
+#define MINFER_ATTN_FLAG_SIMPLE_KERNEL 1
+
 /* error codes */
 #define MINFER_ATTN_OK            0
 #define MINFER_ATTN_EINVAL        1  /* bad shape / stride / pointer / dtype        */
@@ -88,7 +94,7 @@ typedef struct MinferAttnPrefillParams {
   int32_t dtype;          /* MINFER_ATTN_F16 / MINFER_ATTN_BF16 */
   int32_t causal;
   float   softmax_scale;
-  int32_t flags;          /* reserved, pass 0 */
+  int32_t flags;          /* 0, or MINFER_ATTN_FLAG_* */
 } MinferAttnPrefillParams;
 
 int minfer_attn_prefill(const MinferAttnPrefillParams* params, void* stream);
@@ -169,6 +175,9 @@ int32_t minfer_attn_decode_default_chunk(int32_t batch, int32_t n_kv_heads,
 int minfer_attn_decode_static(const MinferAttnDecodeParams* params, void* stream);
 
 const char* minfer_attn_strerror(int code);
+/* Text of the CUDA error behind the calling thread's latest MINFER_ATTN_ECUDA
+ * from a launch ("no error" if none). */
+const char* minfer_attn_last_cuda_error(void);
 int minfer_attn_abi_version(void);
 
 #ifdef __cplusplus

@@ -76,6 +76,13 @@ int make_tensor_map(CUtensorMap* tm, const void* base, bool bf16, int head_dim, 
   return r == CUDA_SUCCESS ? MINFER_ATTN_OK : MINFER_ATTN_EINVAL;
 }
 
+thread_local cudaError_t g_last_cuda_error = cudaSuccess;
+
+int cuda_result(cudaError_t e) {
+  g_last_cuda_error = e;
+  return e == cudaSuccess ? MINFER_ATTN_OK : MINFER_ATTN_ECUDA;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 bool strides_ok(const int64_t* s, int n) {
@@ -100,6 +107,8 @@ using namespace minfer_attn;
 extern "C" {
 
 int minfer_attn_abi_version(void) { return MINFER_ATTN_ABI_VERSION; }
+
+const char* minfer_attn_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda_error); }
 
 const char* minfer_attn_strerror(int code) {
   switch (code) {
@@ -156,8 +165,11 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
   const float scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->head_dim));
   a.scale_log2 = scale * 1.4426950408889634f;
 
-  cudaError_t e = launch_prefill(tq, tk, tv, a, p->head_dim, bf16, static_cast<cudaStream_t>(stream));
-  return e == cudaSuccess ? MINFER_ATTN_OK : MINFER_ATTN_ECUDA;
+  a.pair_heads = (a.group % 2 == 0) ? 1 : 0;
+  cudaError_t e = (p->flags & MINFER_ATTN_FLAG_SIMPLE_KERNEL)
+                      ? launch_prefill(tq, tk, tv, a, p->head_dim, bf16, static_cast<cudaStream_t>(stream))
+                      : launch_prefill_ws(tq, tk, tv, a, p->head_dim, bf16, static_cast<cudaStream_t>(stream));
+  return cuda_result(e);
 }
 
 int32_t minfer_attn_decode_default_chunk(int32_t batch, int32_t n_kv_heads, int32_t max_len) {
@@ -222,7 +234,7 @@ int minfer_attn_decode(const MinferAttnDecodeParams* p, void* stream) {
   a.scale_log2 = scale * 1.4426950408889634f;
 
   cudaError_t e = launch_decode(a, p->head_dim, p->dtype == MINFER_ATTN_BF16, static_cast<cudaStream_t>(stream));
-  return e == cudaSuccess ? MINFER_ATTN_OK : MINFER_ATTN_ECUDA;
+  return cuda_result(e);
 }
 
 }  // extern "C"

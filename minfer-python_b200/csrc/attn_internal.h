@@ -21,6 +21,7 @@ struct PrefillArgs {
   int32_t group;          // query heads per kv head
   int32_t causal;
   int32_t mask_vec;       // mask rows may be read with 16-byte loads
+  int32_t pair_heads;     // two-tile kernel: slots are two heads of one kv head (else two row tiles)
   float scale_log2;       // softmax scale * log2(e)
   // position (1..3) of the batch / head / row coordinate inside each tensor
   // map; coordinate 0 is always head_dim
@@ -29,6 +30,8 @@ struct PrefillArgs {
 };
 
 size_t prefill_smem_bytes(int head_dim);
+cudaError_t launch_prefill_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                              const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream);
 cudaError_t launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillArgs& a,
                            int head_dim, bool bf16, cudaStream_t stream);
 

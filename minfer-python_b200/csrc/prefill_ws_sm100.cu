@@ -1,0 +1,457 @@
+// Warp-specialised prefill attention for sm_100a: two 128-row query tiles per
+// CTA ping-pong on the tensor core so that the softmax of one tile overlaps the
+// MMAs of the other.
+//
+// Fills the launch the reference leaves unimplemented
+// (src/minfer/kernels/torch_ext/csrc/cuda/flash_attn/op.cuh:105; empty kernel at
+// .../flash_attn/kernels/kernel.cuh:16-27).
+//
+// Work of one CTA: two "slots".  With an even GQA group the slots are two query
+// heads of one kv head at the same 128 rows (identical key ranges); otherwise
+// they are two consecutive 128-row tiles of one head.  Both slots share every
+// K/V tile the CTA loads.
+//
+// Roles (384 threads = 3 warpgroups; the third gives registers to the first two
+// with setmaxnreg):
+//   warps 0-3  softmax of slot 0 (thread t owns score row t = TMEM lane t)
+//   warps 4-7  softmax of slot 1
+//   warp  8    lane 0 issues every tcgen05.mma / tcgen05.commit
+//   warp  9    lane 0 issues every TMA load (no multicast)
+//   warps 10-11 idle
+// Tensor memory (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [384,384+D).
+// P (16-bit) overwrites the first 64 columns of its S region and is read by the
+// PV MMA straight from tensor memory (A operand in TMEM), V is the B operand as
+// an MN-major shared-memory descriptor.
+// Shared memory: Q 2 x D/64 blocks, then a ring of kStages K/V tiles; every
+// block is [128 rows x 128 bytes] with the 128-byte swizzle TMA writes.
+//
+// Issue order of the MMA thread:  S0(0) S1(0) | PV0(0) S0(1) | PV1(0) S1(1) | ...
+// so softmax of slot s for key tile j+1 runs while the tensor core works for
+// the other slot.  O is rescaled lazily: a row's reference maximum only moves
+// when the new maximum exceeds it by more than 2^8, so P stays below 256 and
+// most key tiles need no pass over O at all.
+#include "attn_internal.h"
+#include "ptx.cuh"
+
+namespace minfer_attn {
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 128;
+constexpr int kBlockBytes = 128 * 128;
+constexpr int kThreads = 384;  // three warpgroups: softmax 0, softmax 1, MMA + TMA (+ 2 idle warps)
+// register budget per thread after the role split (the launch budget is 65536 / 384 = 168)
+constexpr int kRegsSoftmax = 216;
+constexpr int kRegsOther = 72;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+// barrier indices
+constexpr int kQFull = 0;                 // [2]
+constexpr int kSFull = 2;                 // [2]
+constexpr int kPFull = 4;                 // [2]
+constexpr int kODone = 6;                 // [2]
+constexpr int kKvFull = 8;                // [kStages], then kKvEmpty [kStages]
+
+__device__ __forceinline__ void report_ws(int32_t* status, int site) {
+  if (status != nullptr && atomicCAS(status, 0, kStatusWaitTimeout) == 0) {
+    status[1] = static_cast<int32_t>(blockIdx.x);
+    status[2] = static_cast<int32_t>(blockIdx.y + gridDim.y * blockIdx.z);
+    status[3] = site;
+  }
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const PrefillArgs a) {
+  constexpr int kDB = D / 64;
+  constexpr int kTileBytes = kDB * kBlockBytes;  // one Q, K or V tile
+  // ring depth: 4 tiles at D=128; 8 at D=64, which also keeps the CTA above half
+  // of the shared memory so that two CTAs never compete for the 512 TMEM columns
+  constexpr int kStages = (D == 128) ? 4 : 8;
+  constexpr int kKvEmpty = kKvFull + kStages;
+  constexpr int kNumBars = kKvFull + 2 * kStages;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kIdescS = umma_idesc(kTileM, kTileN, BF16, false, false);
+  constexpr uint32_t kIdescO = umma_idesc(kTileM, D, BF16, false, true);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* s_q = smem;                       // [2][kTileBytes]
+  uint8_t* s_kv = s_q + 2 * kTileBytes;      // [kStages][kTileBytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_kv + kStages * kTileBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int b = blockIdx.z;
+  const int off = a.seq_k - a.seq_q;
+
+  // ---- slot geometry ----
+  int head[2], q0[2], n_tiles[2];
+  {
+    const int xr = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long tiles first
+    if (a.pair_heads) {
+      head[0] = 2 * blockIdx.y;
+      head[1] = head[0] + 1;
+      q0[0] = q0[1] = xr * kTileM;
+    } else {
+      head[0] = head[1] = blockIdx.y;
+      q0[0] = 2 * xr * kTileM;
+      q0[1] = q0[0] + kTileM;
+    }
+    const int n_all = (a.seq_k + kTileN - 1) / kTileN;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      if (q0[s] >= a.seq_q) {
+        n_tiles[s] = 0;
+      } else if (a.causal) {
+        const int last_row = min(q0[s] + kTileM - 1, a.seq_q - 1);
+        n_tiles[s] = min(n_all, (last_row + off) / kTileN + 1);
+      } else {
+        n_tiles[s] = n_all;
+      }
+    }
+  }
+  const int kvh = head[0] / a.group;
+  const int n_max = max(n_tiles[0], n_tiles[1]);
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[kQFull + i], 1);
+      mbar_init(&bars[kSFull + i], 1);
+      mbar_init(&bars[kPFull + i], 128);
+      mbar_init(&bars[kODone + i], 1);
+    }
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&bars[kKvFull + i], 1);
+      mbar_init(&bars[kKvEmpty + i], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp >= 8) {
+    // third warpgroup: hand registers to the softmax warpgroups
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+  if (warp == 9) {
+    // ====================================================================
+    // TMA producer
+    // ====================================================================
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      // coordinate slot i (1..3) of a tensor map holds batch, head or row
+      auto pick = [](int i, const int32_t* pos, int vb, int vh, int vr) {
+        return pos[0] == i ? vb : (pos[1] == i ? vh : vr);
+      };
+      auto load_tile = [&](const CUtensorMap* tm, uint32_t dst, uint64_t* bar, const int32_t* pos, int hh, int row) {
+        const int c1 = pick(1, pos, b, hh, row), c2 = pick(2, pos, b, hh, row), c3 = pick(3, pos, b, hh, row);
+        mbar_arrive_expect_tx(bar, kTileBytes);
+        for (int db = 0; db < kDB; ++db)
+          tma_load_4d_addr(dst + db * kBlockBytes, tm, bar, db * 64, c1, c2, c3);
+      };
+      const uint32_t q_addr = smem_u32(s_q), kv_addr = smem_u32(s_kv);
+      if (n_tiles[0] > 0) load_tile(&tm_q, q_addr, &bars[kQFull + 0], a.q_pos, head[0], q0[0]);
+      if (n_tiles[1] > 0) load_tile(&tm_q, q_addr + kTileBytes, &bars[kQFull + 1], a.q_pos, head[1], q0[1]);
+      bool ok = true;
+      int r_done = 0;
+      const int n_loads = 2 * n_max;  // K0 V0 K1 V1 ...
+      for (int r = 0; r < n_loads; ++r) {
+        const int st = r % kStages;
+        if (r >= kStages) {
+          if (!(ok = mbar_wait(&bars[kKvEmpty + st], ((r / kStages) - 1) & 1, abort_flag))) {
+            report_ws(a.status, 20);
+            break;
+          }
+        }
+        load_tile((r & 1) ? &tm_v : &tm_k, kv_addr + st * kTileBytes, &bars[kKvFull + st], a.kv_pos, kvh,
+                  (r >> 1) * kTileN);
+        r_done = r + 1;
+      }
+      if (!ok || *abort_flag) {
+        // the CTA is giving up: let the copies already issued land before the
+        // shared memory is handed back (bounded polls)
+        for (int i = 0; i < 4000000; ++i) {
+          bool pending = false;
+          if (n_tiles[0] > 0) pending |= !mbar_try_wait(&bars[kQFull + 0], 0);
+          if (n_tiles[1] > 0) pending |= !mbar_try_wait(&bars[kQFull + 1], 0);
+          for (int r = max(0, r_done - kStages); r < r_done; ++r)
+            pending |= !mbar_try_wait(&bars[kKvFull + r % kStages], (r / kStages) & 1);
+          if (!pending) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 8) {
+    // ====================================================================
+    // MMA issuer.  Descriptors are (hi, lo) pairs; only the 14-bit start
+    // address in `lo` changes between instructions.
+    // ====================================================================
+    if (lane == 0) {
+      bool ok = true;
+      constexpr uint32_t kHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+      constexpr uint32_t kLoK = (16u >> 4) << 16;                        // LBO field of the K-major operands
+      constexpr uint32_t kLoV = (static_cast<uint32_t>(kBlockBytes) >> 4) << 16;  // LBO = one block for MN-major V
+      const uint32_t q_lo = (smem_u32(s_q) >> 4) | kLoK;
+      const uint32_t k_lo = (smem_u32(s_kv) >> 4) | kLoK;
+      const uint32_t v_lo = (smem_u32(s_kv) >> 4) | kLoV;
+      auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+
+      auto issue_s = [&](int s, int st) {
+        const uint32_t qa = q_lo + s * (kTileBytes >> 4);
+        const uint32_t ka = k_lo + st * (kTileBytes >> 4);
+#pragma unroll 1
+        for (int i = 0; i < kDB * 4; ++i) {
+          const uint32_t o = (i >> 2) * (kBlockBytes >> 4) + (i & 3) * 2;  // 32 bytes per 16-element k step
+          umma_ss(tmem_base + s * kTileN, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS, i != 0);
+        }
+        umma_commit(&bars[kSFull + s]);
+      };
+      auto issue_pv = [&](int s, int st, bool accumulate) {
+        const uint32_t va = v_lo + st * (kTileBytes >> 4);
+        const uint32_t tp = tmem_base + s * kTileN;  // P: packed 16-bit pairs, 8 columns per 16 keys
+        const uint32_t to = tmem_base + 256 + s * 128;
+#pragma unroll 1
+        for (int kk = 0; kk < kTileN / 16; ++kk)
+          umma_ts(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO, (accumulate || kk != 0) ? 1u : 0u);
+        umma_commit(&bars[kODone + s]);
+      };
+
+      do {
+        if (n_max == 0) break;
+        if (n_tiles[0] > 0 && !(ok = mbar_wait(&bars[kQFull + 0], 0, abort_flag))) { report_ws(a.status, 30); break; }
+        if (n_tiles[1] > 0 && !(ok = mbar_wait(&bars[kQFull + 1], 0, abort_flag))) { report_ws(a.status, 30); break; }
+        // K0
+        if (!(ok = mbar_wait(&bars[kKvFull + 0], 0, abort_flag))) { report_ws(a.status, 31); break; }
+        tc_fence_after();
+        if (n_tiles[0] > 0) issue_s(0, 0);
+        if (n_tiles[1] > 0) issue_s(1, 0);
+        umma_commit(&bars[kKvEmpty + 0]);
+
+        for (int j = 0; j < n_max && ok; ++j) {
+          const int rv = 2 * j + 1;  // ring index of V_j
+          const int rk = 2 * j + 2;  // ring index of K_{j+1}
+          const int stv = rv % kStages, stk = rk % kStages;
+          if (!(ok = mbar_wait(&bars[kKvFull + stv], (rv / kStages) & 1, abort_flag))) { report_ws(a.status, 32); break; }
+          bool k_waited = false;
+#pragma unroll 1
+          for (int s = 0; s < 2; ++s) {
+            const int nts = s ? n_tiles[1] : n_tiles[0];
+            if (j >= nts) continue;
+            if (!(ok = mbar_wait(&bars[kPFull + s], j & 1, abort_flag))) { report_ws(a.status, 33); break; }
+            tc_fence_after();
+            issue_pv(s, stv, j > 0);
+            if (j + 1 < nts) {
+              if (!k_waited) {
+                if (!(ok = mbar_wait(&bars[kKvFull + stk], (rk / kStages) & 1, abort_flag))) { report_ws(a.status, 34); break; }
+                k_waited = true;
+                tc_fence_after();
+              }
+              issue_s(s, stk);
+            }
+          }
+          if (!ok) break;
+          umma_commit(&bars[kKvEmpty + stv]);
+          if (j + 1 < n_max) umma_commit(&bars[kKvEmpty + stk]);
+        }
+      } while (false);
+    }
+    __syncwarp();
+  }
+  } else {
+    // ====================================================================
+    // softmax (+ lazy correction + epilogue) of slot s
+    // ====================================================================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+    const int s = warp >> 2;
+    const int row = tid & 127;
+    const int q0s = s ? q0[1] : q0[0];
+    const int heads = s ? head[1] : head[0];
+    const int r_glob = q0s + row;
+    const uint32_t t_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + s * kTileN + t_lane;
+    const uint32_t tmem_o = tmem_base + 256 + s * 128 + t_lane;
+    const float sl2 = a.scale_log2;
+    const int nt = s ? n_tiles[1] : n_tiles[0];
+    float m_ref = -INFINITY;  // reference maximum the stored P and O are relative to
+    float l_run = 0.f;
+    bool ok = true;
+    const uint8_t* mrow =
+        (a.mask && nt > 0) ? a.mask + (static_cast<size_t>(b) * a.seq_q + min(r_glob, a.seq_q - 1)) * a.seq_k : nullptr;
+
+    for (int j = 0; j < nt; ++j) {
+      const int kv0 = j * kTileN;
+      if (!(ok = mbar_wait(&bars[kSFull + s], j & 1, abort_flag))) { report_ws(a.status, 40); break; }
+      tc_fence_after();
+
+      uint32_t sr[kTileN];
+#pragma unroll
+      for (int c = 0; c < kTileN / 32; ++c)
+        tmem_ld32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
+      tc_wait_ld();
+
+      // ---- masking (tile-uniform decision) ----
+      const bool tail = kv0 + kTileN > a.seq_k;
+      const bool diag = a.causal && (kv0 + kTileN - 1 > q0s + off);
+      if (mrow != nullptr) {
+        if (!tail && a.mask_vec) {
+          const uint4* mp = reinterpret_cast<const uint4*>(mrow + kv0);
+#pragma unroll
+          for (int c = 0; c < kTileN / 16; ++c) {
+            const uint4 mv = __ldg(mp + c);
+            const uint32_t w[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              if (((w[e >> 2] >> ((e & 3) * 8)) & 0xFFu) == 0) sr[c * 16 + e] = 0xFF800000u;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < kTileN; ++c) {
+            const int col = kv0 + c;
+            const bool vis = col < a.seq_k && mrow[col] != 0;
+            if (!vis) sr[c] = 0xFF800000u;
+          }
+        }
+      } else if (tail || diag) {
+        const int lim = a.causal ? min(a.seq_k - 1, r_glob + off) : a.seq_k - 1;
+#pragma unroll
+        for (int c = 0; c < kTileN; ++c)
+          if (kv0 + c > lim) sr[c] = 0xFF800000u;
+      }
+
+      // ---- row maximum; move the reference only when it lags by > 2^8 ----
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < kTileN; c += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sr[c]));
+        mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      const bool move = (mx != -INFINITY) && (m_ref == -INFINITY || (mx - m_ref) * sl2 > kRescaleThreshold);
+      if (__any_sync(0xFFFFFFFFu, move)) {
+        const float alpha = (move && m_ref != -INFINITY) ? ex2_approx((m_ref - mx) * sl2) : 1.f;
+        if (move) m_ref = mx;
+        l_run *= alpha;
+        if (j > 0) {
+          // PV(j-1) of this slot must have landed before O is touched
+          if (!(ok = mbar_wait(&bars[kODone + s], (j - 1) & 1, abort_flag))) { report_ws(a.status, 41); break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem_o + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st32(tmem_o + c * 32, o);
+          }
+        }
+      }
+
+      // ---- P = exp2(S*c - m*c) -> 16-bit pairs -> tensor memory (over S) ----
+      const float mb = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < kTileN / 32; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * e]), sl2, -mb));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * e + 1]), sl2, -mb));
+          sum0 += p0;
+          sum1 += p1;
+          pk[e] = pack2<BF16>(p0, p1);
+        }
+        tmem_st16(tmem_s + c * 16, pk);
+      }
+      l_run += sum0 + sum1;
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bars[kPFull + s]);
+    }
+
+    // ---- epilogue: O / l -> out ----
+    if (ok && nt > 0) {
+      if (!(ok = mbar_wait(&bars[kODone + s], (nt - 1) & 1, abort_flag))) report_ws(a.status, 42);
+    }
+    if (ok && nt > 0) {
+      tc_fence_after();
+      const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
+      const bool row_valid = r_glob < a.seq_q;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) +
+                      2 * (static_cast<size_t>(b) * a.out_stride[0] + static_cast<size_t>(heads) * a.out_stride[1] +
+                           static_cast<size_t>(min(r_glob, a.seq_q - 1)) * a.out_stride[2]);
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tmem_o + c * 32, o);
+        tc_wait_ld();
+        if (row_valid) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 w;
+            w.x = pack2<BF16>(__uint_as_float(o[q4 * 8 + 0]) * inv, __uint_as_float(o[q4 * 8 + 1]) * inv);
+            w.y = pack2<BF16>(__uint_as_float(o[q4 * 8 + 2]) * inv, __uint_as_float(o[q4 * 8 + 3]) * inv);
+            w.z = pack2<BF16>(__uint_as_float(o[q4 * 8 + 4]) * inv, __uint_as_float(o[q4 * 8 + 5]) * inv);
+            w.w = pack2<BF16>(__uint_as_float(o[q4 * 8 + 6]) * inv, __uint_as_float(o[q4 * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + (c * 32 + q4 * 8) * 2) = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int D, bool BF16>
+cudaError_t launch_ws_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillArgs& a,
+                          cudaStream_t stream) {
+  constexpr int kStages = (D == 128) ? 4 : 8;
+  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 512 + 1024;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 64 && !attr_done[dev]) {
+    e = cudaFuncSetAttribute(prefill_ws_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    attr_done[dev] = true;
+  }
+  const int n_qt = (a.seq_q + kTileM - 1) / kTileM;
+  dim3 grid = a.pair_heads ? dim3(n_qt, a.n_heads / 2, a.batch) : dim3((n_qt + 1) / 2, a.n_heads, a.batch);
+  prefill_ws_kernel<D, BF16><<<grid, kThreads, smem, stream>>>(tq, tk, tv, a);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_prefill_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                              const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream) {
+  if (head_dim == 128)
+    return bf16 ? launch_ws_one<128, true>(tq, tk, tv, a, stream) : launch_ws_one<128, false>(tq, tk, tv, a, stream);
+  return bf16 ? launch_ws_one<64, true>(tq, tk, tv, a, stream) : launch_ws_one<64, false>(tq, tk, tv, a, stream);
+}
+
+}  // namespace minfer_attn

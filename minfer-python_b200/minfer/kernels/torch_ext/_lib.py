@@ -21,6 +21,7 @@ EXPORTS = (
     "minfer_attn_decode_workspace_bytes",
     "minfer_attn_decode_default_chunk",
     "minfer_attn_strerror",
+    "minfer_attn_last_cuda_error",
     "minfer_attn_abi_version",
 )
 
@@ -91,6 +92,8 @@ def _load() -> ctypes.CDLL:
     lib.minfer_attn_decode_default_chunk.restype = ctypes.c_int32
     lib.minfer_attn_strerror.argtypes = [ctypes.c_int]
     lib.minfer_attn_strerror.restype = ctypes.c_char_p
+    lib.minfer_attn_last_cuda_error.argtypes = []
+    lib.minfer_attn_last_cuda_error.restype = ctypes.c_char_p
     lib.minfer_attn_abi_version.argtypes = []
     lib.minfer_attn_abi_version.restype = ctypes.c_int
     return lib
@@ -105,4 +108,5 @@ def strerror(code: int) -> str:
 
 def check(code: int, what: str) -> None:
     if code != 0:
-        raise RuntimeError(f"{what}: {strerror(code)} (code {code})")
+        detail = f" [{lib.minfer_attn_last_cuda_error().decode()}]" if code == 3 else ""
+        raise RuntimeError(f"{what}: {strerror(code)} (code {code}){detail}")

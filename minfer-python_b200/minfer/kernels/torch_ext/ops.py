@@ -18,6 +18,8 @@ import torch
 from . import _lib
 
 _DEBUG = os.environ.get("MINFER_ATTN_DEBUG", "0") not in ("", "0")
+# cross-check aid: run the single-tile prefill kernel instead of the two-tile one
+_SIMPLE = os.environ.get("MINFER_ATTN_SIMPLE_KERNEL", "0") not in ("", "0")
 
 _DEFS = {
     "flash_attn": "(int qtype_int, int qblock_size, int qtype_size, Tensor q, Tensor k, Tensor v, "
@@ -89,7 +91,7 @@ def _prefill(q, k, v, mask, out, causal: bool) -> None:
     p.dtype = _dtype_tag(q)
     p.causal = 1 if causal else 0
     p.softmax_scale = 0.0
-    p.flags = 0
+    p.flags = 1 if _SIMPLE else 0
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
         _lib.check(_lib.lib.minfer_attn_prefill(ctypes.byref(p), ctypes.c_void_p(stream)), "minfer_attn_prefill")
