@@ -53,6 +53,19 @@ constexpr int kPFull = 4;                 // [2]
 constexpr int kODone = 6;                 // [2]
 constexpr int kKvFull = 8;                // [kStages], then kKvEmpty [kStages]
 
+// Optional timeline for tuning (compiled in only with -DMINFER_ATTN_TRACE): the
+// roles of one CTA write clock64() stamps behind the 16 status words.
+#ifdef MINFER_ATTN_TRACE
+#define WS_TRACE(role, idx, ev)                                                                        \
+  do {                                                                                                 \
+    if (trace_on && (idx) < 64) trace_buf[((role) * 64 + (idx)) * 8 + (ev)] = clock64();              \
+  } while (0)
+#else
+#define WS_TRACE(role, idx, ev) \
+  do {                          \
+  } while (0)
+#endif
+
 __device__ __forceinline__ void report_ws(int32_t* status, int site) {
   if (status != nullptr && atomicCAS(status, 0, kStatusWaitTimeout) == 0) {
     status[1] = static_cast<int32_t>(blockIdx.x);
@@ -118,6 +131,10 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
   const int kvh = head[0] / a.group;
   const int n_max = max(n_tiles[0], n_tiles[1]);
+#ifdef MINFER_ATTN_TRACE
+  const bool trace_on = a.status != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid & 127) == 0;
+  long long* trace_buf = reinterpret_cast<long long*>(a.status + 16);
+#endif
 
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -210,13 +227,18 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint32_t v_lo = (smem_u32(s_kv) >> 4) | kLoV;
       auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
 
+      // Fully unrolled on purpose: the issuing thread must feed one MMA per ~64
+      // tensor-core cycles, so each issue may only cost a handful of instructions
+      // (one add per descriptor; everything else is an immediate).
       auto issue_s = [&](int s, int st) {
         const uint32_t qa = q_lo + s * (kTileBytes >> 4);
         const uint32_t ka = k_lo + st * (kTileBytes >> 4);
-#pragma unroll 1
+        const uint32_t ts = tmem_base + s * kTileN;
+#pragma unroll
         for (int i = 0; i < kDB * 4; ++i) {
           const uint32_t o = (i >> 2) * (kBlockBytes >> 4) + (i & 3) * 2;  // 32 bytes per 16-element k step
-          umma_ss(tmem_base + s * kTileN, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS, i != 0);
+          if (i == 0) umma_ss_first(ts, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
+          else umma_ss_acc(ts, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
         }
         umma_commit(&bars[kSFull + s]);
       };
@@ -224,9 +246,9 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t va = v_lo + st * (kTileBytes >> 4);
         const uint32_t tp = tmem_base + s * kTileN;  // P: packed 16-bit pairs, 8 columns per 16 keys
         const uint32_t to = tmem_base + 256 + s * 128;
-#pragma unroll 1
-        for (int kk = 0; kk < kTileN / 16; ++kk)
-          umma_ts(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO, (accumulate || kk != 0) ? 1u : 0u);
+        umma_ts(to, tp, desc(va, kHi), kIdescO, accumulate ? 1u : 0u);
+#pragma unroll
+        for (int kk = 1; kk < kTileN / 16; ++kk) umma_ts_acc(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO);
         umma_commit(&bars[kODone + s]);
       };
 
@@ -251,7 +273,9 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           for (int s = 0; s < 2; ++s) {
             const int nts = s ? n_tiles[1] : n_tiles[0];
             if (j >= nts) continue;
+            WS_TRACE(2, j, s * 3 + 0);
             if (!(ok = mbar_wait(&bars[kPFull + s], j & 1, abort_flag))) { report_ws(a.status, 33); break; }
+            WS_TRACE(2, j, s * 3 + 1);
             tc_fence_after();
             issue_pv(s, stv, j > 0);
             if (j + 1 < nts) {
@@ -262,6 +286,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
               }
               issue_s(s, stk);
             }
+            WS_TRACE(2, j, s * 3 + 2);
           }
           if (!ok) break;
           umma_commit(&bars[kKvEmpty + stv]);
@@ -294,7 +319,9 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
     for (int j = 0; j < nt; ++j) {
       const int kv0 = j * kTileN;
+      WS_TRACE(s, j, 0);
       if (!(ok = mbar_wait(&bars[kSFull + s], j & 1, abort_flag))) { report_ws(a.status, 40); break; }
+      WS_TRACE(s, j, 1);
       tc_fence_after();
 
       uint32_t sr[kTileN];
@@ -302,6 +329,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int c = 0; c < kTileN / 32; ++c)
         tmem_ld32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
       tc_wait_ld();
+      WS_TRACE(s, j, 2);
 
       // ---- masking (tile-uniform decision) ----
       const bool tail = kv0 + kTileN > a.seq_k;
@@ -335,11 +363,11 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // ---- row maximum; move the reference only when it lags by > 2^8 ----
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < kTileN; c += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(sr[c]));
-        mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
+      for (int c = 0; c < kTileN; c += 8) {
+        mx0 = fmax3(mx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+        mx2 = fmax3(mx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
+        mx3 = fmax3(mx3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const bool move = (mx != -INFINITY) && (m_ref == -INFINITY || (mx - m_ref) * sl2 > kRescaleThreshold);
@@ -363,6 +391,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
 
+      WS_TRACE(s, j, 3);
       // ---- P = exp2(S*c - m*c) -> 16-bit pairs -> tensor memory (over S) ----
       const float mb = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
       float sum0 = 0.f, sum1 = 0.f;
@@ -380,9 +409,11 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tmem_st16(tmem_s + c * 16, pk);
       }
       l_run += sum0 + sum1;
+      WS_TRACE(s, j, 4);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&bars[kPFull + s]);
+      WS_TRACE(s, j, 5);
     }
 
     // ---- epilogue: O / l -> out ----
