@@ -45,6 +45,10 @@ constexpr int kThreads = 384;  // three warpgroups: softmax 0, softmax 1, MMA + 
 constexpr int kRegsSoftmax = 216;
 constexpr int kRegsOther = 72;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef MINFER_ATTN_POLY_OF_8
+#define MINFER_ATTN_POLY_OF_8 2
+#endif
+constexpr int kPolyOf8 = MINFER_ATTN_POLY_OF_8;  // share of exp2 evaluations done without the SFU
 
 // barrier indices
 constexpr int kQFull = 0;                 // [2]
@@ -132,7 +136,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int kvh = head[0] / a.group;
   const int n_max = max(n_tiles[0], n_tiles[1]);
 #ifdef MINFER_ATTN_TRACE
-  const bool trace_on = a.status != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid & 127) == 0;
+  const bool trace_on = a.status != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid & 127) == 0;  // thread 256 = lane 0 of the MMA warp
   long long* trace_buf = reinterpret_cast<long long*>(a.status + 16);
 #endif
 
@@ -166,19 +170,26 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // ====================================================================
     // TMA producer
     // ====================================================================
-    if (lane == 0) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
+    // The whole warp runs the loops (so addresses and coordinates stay in the
+    // uniform datapath); one elected lane issues the copies.
+    const bool leader = elect_one() != 0;
+    {
+      if (leader) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+      }
       // coordinate slot i (1..3) of a tensor map holds batch, head or row
       auto pick = [](int i, const int32_t* pos, int vb, int vh, int vr) {
         return pos[0] == i ? vb : (pos[1] == i ? vh : vr);
       };
       auto load_tile = [&](const CUtensorMap* tm, uint32_t dst, uint64_t* bar, const int32_t* pos, int hh, int row) {
         const int c1 = pick(1, pos, b, hh, row), c2 = pick(2, pos, b, hh, row), c3 = pick(3, pos, b, hh, row);
-        mbar_arrive_expect_tx(bar, kTileBytes);
-        for (int db = 0; db < kDB; ++db)
-          tma_load_4d_addr(dst + db * kBlockBytes, tm, bar, db * 64, c1, c2, c3);
+        if (leader) {
+          mbar_arrive_expect_tx(bar, kTileBytes);
+#pragma unroll
+          for (int db = 0; db < kDB; ++db) tma_load_4d_addr(dst + db * kBlockBytes, tm, bar, db * 64, c1, c2, c3);
+        }
       };
       const uint32_t q_addr = smem_u32(s_q), kv_addr = smem_u32(s_kv);
       if (n_tiles[0] > 0) load_tile(&tm_q, q_addr, &bars[kQFull + 0], a.q_pos, head[0], q0[0]);
@@ -217,7 +228,11 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // MMA issuer.  Descriptors are (hi, lo) pairs; only the 14-bit start
     // address in `lo` changes between instructions.
     // ====================================================================
-    if (lane == 0) {
+    // Converged warp; one elected lane issues.  Keeping the control flow and the
+    // descriptor arithmetic warp-uniform lets them live in uniform registers,
+    // which is what tcgen05.mma takes its descriptors from.
+    const bool leader = elect_one() != 0;
+    {
       bool ok = true;
       constexpr uint32_t kHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
       constexpr uint32_t kLoK = (16u >> 4) << 16;                        // LBO field of the K-major operands
@@ -237,19 +252,22 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
         for (int i = 0; i < kDB * 4; ++i) {
           const uint32_t o = (i >> 2) * (kBlockBytes >> 4) + (i & 3) * 2;  // 32 bytes per 16-element k step
-          if (i == 0) umma_ss_first(ts, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
-          else umma_ss_acc(ts, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
+          if (leader) {
+            if (i == 0) umma_ss_first(ts, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
+            else umma_ss_acc(ts, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
+          }
         }
-        umma_commit(&bars[kSFull + s]);
+        if (leader) umma_commit(&bars[kSFull + s]);
       };
       auto issue_pv = [&](int s, int st, bool accumulate) {
         const uint32_t va = v_lo + st * (kTileBytes >> 4);
         const uint32_t tp = tmem_base + s * kTileN;  // P: packed 16-bit pairs, 8 columns per 16 keys
         const uint32_t to = tmem_base + 256 + s * 128;
-        umma_ts(to, tp, desc(va, kHi), kIdescO, accumulate ? 1u : 0u);
+        if (leader) umma_ts(to, tp, desc(va, kHi), kIdescO, accumulate ? 1u : 0u);
 #pragma unroll
-        for (int kk = 1; kk < kTileN / 16; ++kk) umma_ts_acc(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO);
-        umma_commit(&bars[kODone + s]);
+        for (int kk = 1; kk < kTileN / 16; ++kk)
+          if (leader) umma_ts_acc(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO);
+        if (leader) umma_commit(&bars[kODone + s]);
       };
 
       do {
@@ -261,7 +279,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tc_fence_after();
         if (n_tiles[0] > 0) issue_s(0, 0);
         if (n_tiles[1] > 0) issue_s(1, 0);
-        umma_commit(&bars[kKvEmpty + 0]);
+        if (leader) umma_commit(&bars[kKvEmpty + 0]);
 
         for (int j = 0; j < n_max && ok; ++j) {
           const int rv = 2 * j + 1;  // ring index of V_j
@@ -289,8 +307,10 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             WS_TRACE(2, j, s * 3 + 2);
           }
           if (!ok) break;
-          umma_commit(&bars[kKvEmpty + stv]);
-          if (j + 1 < n_max) umma_commit(&bars[kKvEmpty + stk]);
+          if (leader) {
+            umma_commit(&bars[kKvEmpty + stv]);
+            if (j + 1 < n_max) umma_commit(&bars[kKvEmpty + stk]);
+          }
         }
       } while (false);
     }
@@ -394,21 +414,31 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       WS_TRACE(s, j, 3);
       // ---- P = exp2(S*c - m*c) -> 16-bit pairs -> tensor memory (over S) ----
       const float mb = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
-      float sum0 = 0.f, sum1 = 0.f;
+      const float2 sl2_2 = make_float2(sl2, sl2);
+      const float2 nmb_2 = make_float2(-mb, -mb);
+      float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < kTileN / 32; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * e]), sl2, -mb));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * e + 1]), sl2, -mb));
-          sum0 += p0;
-          sum1 += p1;
-          pk[e] = pack2<BF16>(p0, p1);
+          const float2 sp = make_float2(__uint_as_float(sr[c * 32 + 2 * e]), __uint_as_float(sr[c * 32 + 2 * e + 1]));
+          const float2 x = __ffma2_rn(sp, sl2_2, nmb_2);
+          float2 p;
+          // kPolyOf8 of every 8 pairs go through the FMA-pipe polynomial, the rest
+          // through the special-function unit, so both units stay busy
+          if ((e & 7) < kPolyOf8) {
+            p = ex2_poly2(x);
+          } else {
+            p.x = ex2_approx(x.x);
+            p.y = ex2_approx(x.y);
+          }
+          sum2 = __fadd2_rn(sum2, p);
+          pk[e] = pack2<BF16>(p.x, p.y);
         }
         tmem_st16(tmem_s + c * 16, pk);
       }
-      l_run += sum0 + sum1;
+      l_run += sum2.x + sum2.y;
       WS_TRACE(s, j, 4);
       tc_wait_st();
       tc_fence_before();

@@ -9,7 +9,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libminfer_attn.so")
+# MINFER_ATTN_LIBRARY points at another build of the same library (e.g. one compiled with tuning macros)
+LIB_PATH = os.environ.get("MINFER_ATTN_LIBRARY") or os.path.join(_HERE, "libminfer_attn.so")
 
 F16 = 0
 BF16 = 1
