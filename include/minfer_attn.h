@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define MINFER_ATTN_ABI_VERSION 1
+#define MINFER_ATTN_ABI_VERSION 2
 
 /* element types of q/k/v/out */
 #define MINFER_ATTN_F16  0
@@ -95,9 +95,22 @@ typedef struct MinferAttnPrefillParams {
   int32_t causal;
   float   softmax_scale;
   int32_t flags;          /* 0, or MINFER_ATTN_FLAG_* */
+  void*   workspace;      /* optional device scratch for dense masks, see below */
+  size_t  workspace_bytes;
 } MinferAttnPrefillParams;
 
 int minfer_attn_prefill(const MinferAttnPrefillParams* params, void* stream);
+
+/*
+ * Scratch for calls with a dense mask.  When `workspace` holds at least this
+ * many bytes, one pass over the mask classifies its 128 x 128 tiles (nothing
+ * visible / everything visible / mixed); the attention kernel then skips tiles
+ * nobody can see and reads mask bytes only for mixed ones, so a dense causal or
+ * sliding-window mask costs about what the structure it encodes costs.  Without
+ * a workspace (NULL) every tile is visited and masked byte by byte: same
+ * result, more time.  Unused by causal calls.  Returns 0 for invalid sizes.
+ */
+size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t seq_k);
 
 /*
  * Decode attention over a padded KV cache (one query token per sequence).

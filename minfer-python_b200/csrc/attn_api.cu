@@ -137,6 +137,8 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
     return MINFER_ATTN_EINVAL;
   if (!(p->softmax_scale >= 0.f)) return MINFER_ATTN_EINVAL;
   if (p->batch > 65535 || p->n_heads > 65535) return MINFER_ATTN_EUNSUPPORTED;
+  // the masked kernel's tile list holds 1024 key tiles
+  if (!p->causal && p->mask != nullptr && p->seq_k > 128 * 1024) return MINFER_ATTN_EUNSUPPORTED;
   int rc = check_device();
   if (rc != MINFER_ATTN_OK) return rc;
 
@@ -153,6 +155,16 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
 
   a.out = p->out;
   a.mask = p->causal ? nullptr : p->mask;
+  a.cls = nullptr;
+  if (a.mask != nullptr) {
+    const size_t need = minfer_attn_prefill_workspace_bytes(p->batch, p->seq_q, p->seq_k);
+    if (p->workspace != nullptr && p->workspace_bytes >= need && !(p->flags & MINFER_ATTN_FLAG_SIMPLE_KERNEL)) {
+      cudaError_t ce = launch_mask_classify(a.mask, static_cast<uint8_t*>(p->workspace), p->batch, p->seq_q, p->seq_k,
+                                            static_cast<cudaStream_t>(stream));
+      if (ce != cudaSuccess) return cuda_result(ce);
+      a.cls = static_cast<const uint8_t*>(p->workspace);
+    }
+  }
   a.status = p->status;
   for (int i = 0; i < 3; ++i) a.out_stride[i] = p->out_stride[i];
   a.batch = p->batch;
@@ -170,6 +182,11 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
                       ? launch_prefill(tq, tk, tv, a, p->head_dim, bf16, static_cast<cudaStream_t>(stream))
                       : launch_prefill_ws(tq, tk, tv, a, p->head_dim, bf16, static_cast<cudaStream_t>(stream));
   return cuda_result(e);
+}
+
+size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t seq_k) {
+  if (batch <= 0 || seq_q <= 0 || seq_k <= 0) return 0;
+  return static_cast<size_t>(batch) * ((seq_q + 127) / 128) * ((seq_k + 127) / 128);
 }
 
 int32_t minfer_attn_decode_default_chunk(int32_t batch, int32_t n_kv_heads, int32_t max_len) {

@@ -15,6 +15,7 @@ constexpr int32_t kStatusWaitTimeout = 100;
 struct PrefillArgs {
   void* out;
   const uint8_t* mask;
+  const uint8_t* cls;     // per (batch, query tile, key tile) mask class, or null: see mask_classify.cu
   int32_t* status;
   int64_t out_stride[3];  // elements: batch, head, row
   int32_t batch, n_heads, seq_q, seq_k;
@@ -34,6 +35,11 @@ cudaError_t launch_prefill_ws(const CUtensorMap& tq, const CUtensorMap& tk, cons
                               const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream);
 cudaError_t launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillArgs& a,
                            int head_dim, bool bf16, cudaStream_t stream);
+
+// Classifies every 128 x 128 tile of a dense [batch, 1, seq_q, seq_k] byte mask: 0 = no byte set,
+// 1 = every in-range byte set, 2 = mixed.  cls is [batch, ceil(seq_q/128), ceil(seq_k/128)].
+cudaError_t launch_mask_classify(const uint8_t* mask, uint8_t* cls, int batch, int seq_q, int seq_k,
+                                 cudaStream_t stream);
 
 // Kernel-side view of a decode call.
 struct DecodeArgs {

@@ -56,6 +56,8 @@ constexpr int kSFull = 2;                 // [2]
 constexpr int kPFull = 4;                 // [2]
 constexpr int kODone = 6;                 // [2]
 constexpr int kKvFull = 8;                // [kStages], then kKvEmpty [kStages]
+constexpr int kMaxList = 1024;            // key tiles a masked call may have (seq_k <= 131072)
+// per-tile flag bits: slot s visits the tile (1 << 2s), and must read mask bytes for it (2 << 2s)
 
 // Optional timeline for tuning (compiled in only with -DMINFER_ATTN_TRACE): the
 // roles of one CTA write clock64() stamps behind the 16 status words.
@@ -78,7 +80,12 @@ __device__ __forceinline__ void report_ws(int32_t* status, int site) {
   }
 }
 
-template <int D, bool BF16>
+// kMasked = false: causal (or unmasked) attention, the key tiles of a slot are the
+// prefix [0, n_tiles).  kMasked = true: a dense mask; the CTA first compacts the
+// per-tile classes written by mask_classify_kernel (0 = nothing visible, 1 = all
+// visible, 2 = mixed) into a list of the key tiles at least one slot must visit,
+// skips the others entirely and reads mask bytes only for mixed tiles.
+template <int D, bool BF16, bool kMasked>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const PrefillArgs a) {
@@ -100,6 +107,9 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_kv + kStages * kTileBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* n_list = reinterpret_cast<int*>(tmem_slot + 2);
+  uint16_t* u_tile = reinterpret_cast<uint16_t*>(tmem_slot + 4);         // [kMaxList] key tile index
+  uint8_t* u_flag = reinterpret_cast<uint8_t*>(u_tile + kMaxList);      // [kMaxList] visit / needs-mask bits
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -158,10 +168,53 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
+  if constexpr (kMasked) {
+    if (warp == 0) {
+      // compact the tile classes of the two slots into the visit list
+      const int n_kt = (a.seq_k + kTileN - 1) / kTileN;
+      const int n_qt = (a.seq_q + kTileM - 1) / kTileM;
+      const bool act0 = q0[0] < a.seq_q, act1 = q0[1] < a.seq_q;
+      const uint8_t* c0 = (a.cls && act0) ? a.cls + (static_cast<size_t>(b) * n_qt + q0[0] / kTileM) * n_kt : nullptr;
+      const uint8_t* c1 = (a.cls && act1) ? a.cls + (static_cast<size_t>(b) * n_qt + q0[1] / kTileM) * n_kt : nullptr;
+      int count = 0;
+      for (int base = 0; base < n_kt; base += 32) {
+        const int t = base + lane;
+        uint32_t f = 0;
+        if (t < n_kt) {
+          // without a class table every tile counts as mixed
+          const uint32_t k0 = act0 ? (c0 ? c0[t] : 2u) : 0u;
+          const uint32_t k1 = act1 ? (c1 ? c1[t] : 2u) : 0u;
+          if (k0) f |= 1u | (k0 == 2u ? 2u : 0u);
+          if (k1) f |= 4u | (k1 == 2u ? 8u : 0u);
+        }
+        const uint32_t m = __ballot_sync(0xFFFFFFFFu, f != 0);
+        if (f) {
+          const int pos = count + __popc(m & ((1u << lane) - 1u));
+          if (pos < kMaxList) {
+            u_tile[pos] = static_cast<uint16_t>(t);
+            u_flag[pos] = static_cast<uint8_t>(f);
+          }
+        }
+        count += __popc(m);
+      }
+      if (lane == 0) *n_list = min(count, kMaxList);
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // the key tiles this CTA walks, and who visits each
+  const int n_u = kMasked ? *n_list : n_max;
+  auto tile_at = [&](int i) -> int {
+    if constexpr (kMasked) return u_tile[i];
+    else return i;
+  };
+  auto flag_at = [&](int i) -> uint32_t {
+    if constexpr (kMasked) return u_flag[i];
+    else return (i < n_tiles[0] ? 1u : 0u) | (i < n_tiles[1] ? 4u : 0u);
+  };
+  const bool act[2] = {q0[0] < a.seq_q, q0[1] < a.seq_q};
 
   if (warp >= 8) {
     // third warpgroup: hand registers to the softmax warpgroups
@@ -192,11 +245,11 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       };
       const uint32_t q_addr = smem_u32(s_q), kv_addr = smem_u32(s_kv);
-      if (n_tiles[0] > 0) load_tile(&tm_q, q_addr, &bars[kQFull + 0], a.q_pos, head[0], q0[0]);
-      if (n_tiles[1] > 0) load_tile(&tm_q, q_addr + kTileBytes, &bars[kQFull + 1], a.q_pos, head[1], q0[1]);
+      if (act[0] && n_u > 0) load_tile(&tm_q, q_addr, &bars[kQFull + 0], a.q_pos, head[0], q0[0]);
+      if (act[1] && n_u > 0) load_tile(&tm_q, q_addr + kTileBytes, &bars[kQFull + 1], a.q_pos, head[1], q0[1]);
       bool ok = true;
       int r_done = 0;
-      const int n_loads = 2 * n_max;  // K0 V0 K1 V1 ...
+      const int n_loads = 2 * n_u;  // K V K V ... of the listed tiles
       for (int r = 0; r < n_loads; ++r) {
         const int st = r % kStages;
         if (r >= kStages) {
@@ -206,7 +259,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
         load_tile((r & 1) ? &tm_v : &tm_k, kv_addr + st * kTileBytes, &bars[kKvFull + st], a.kv_pos, kvh,
-                  (r >> 1) * kTileN);
+                  tile_at(r >> 1) * kTileN);
         r_done = r + 1;
       }
       if (!ok || *abort_flag) {
@@ -214,8 +267,8 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // shared memory is handed back (bounded polls)
         for (int i = 0; i < 4000000; ++i) {
           bool pending = false;
-          if (n_tiles[0] > 0) pending |= !mbar_try_wait(&bars[kQFull + 0], 0);
-          if (n_tiles[1] > 0) pending |= !mbar_try_wait(&bars[kQFull + 1], 0);
+          if (act[0] && n_u > 0) pending |= !mbar_try_wait(&bars[kQFull + 0], 0);
+          if (act[1] && n_u > 0) pending |= !mbar_try_wait(&bars[kQFull + 1], 0);
           for (int r = max(0, r_done - kStages); r < r_done; ++r)
             pending |= !mbar_try_wait(&bars[kKvFull + r % kStages], (r / kStages) & 1);
           if (!pending) break;
@@ -271,32 +324,43 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       };
 
       do {
-        if (n_max == 0) break;
-        if (n_tiles[0] > 0 && !(ok = mbar_wait(&bars[kQFull + 0], 0, abort_flag))) { report_ws(a.status, 30); break; }
-        if (n_tiles[1] > 0 && !(ok = mbar_wait(&bars[kQFull + 1], 0, abort_flag))) { report_ws(a.status, 30); break; }
-        // K0
+        if (n_u == 0) break;
+        if (act[0] && !(ok = mbar_wait(&bars[kQFull + 0], 0, abort_flag))) { report_ws(a.status, 30); break; }
+        if (act[1] && !(ok = mbar_wait(&bars[kQFull + 1], 0, abort_flag))) { report_ws(a.status, 30); break; }
+        // first listed K tile
         if (!(ok = mbar_wait(&bars[kKvFull + 0], 0, abort_flag))) { report_ws(a.status, 31); break; }
         tc_fence_after();
-        if (n_tiles[0] > 0) issue_s(0, 0);
-        if (n_tiles[1] > 0) issue_s(1, 0);
+        {
+          const uint32_t f0 = flag_at(0);
+          if (f0 & 1u) issue_s(0, 0);
+          if (f0 & 4u) issue_s(1, 0);
+        }
         if (leader) umma_commit(&bars[kKvEmpty + 0]);
 
-        for (int j = 0; j < n_max && ok; ++j) {
-          const int rv = 2 * j + 1;  // ring index of V_j
-          const int rk = 2 * j + 2;  // ring index of K_{j+1}
+        // Per listed tile i and slot s:  PV_s(i) if s visits i, then S_s(i+1) if s
+        // visits i+1.  Only K of the next listed tile is ever needed ahead, so the
+        // ring cannot deadlock however sparse a slot's visits are.
+        uint32_t done[2] = {0u, 0u};  // tiles finished per slot: parity of p_full / first-PV flag
+        for (int i = 0; i < n_u && ok; ++i) {
+          const int rv = 2 * i + 1;  // ring index of V of tile i
+          const int rk = 2 * i + 2;  // ring index of K of tile i+1
           const int stv = rv % kStages, stk = rk % kStages;
+          const uint32_t f = flag_at(i);
+          const uint32_t fn = (i + 1 < n_u) ? flag_at(i + 1) : 0u;
           if (!(ok = mbar_wait(&bars[kKvFull + stv], (rv / kStages) & 1, abort_flag))) { report_ws(a.status, 32); break; }
           bool k_waited = false;
-#pragma unroll 1
+#pragma unroll
           for (int s = 0; s < 2; ++s) {
-            const int nts = s ? n_tiles[1] : n_tiles[0];
-            if (j >= nts) continue;
-            WS_TRACE(2, j, s * 3 + 0);
-            if (!(ok = mbar_wait(&bars[kPFull + s], j & 1, abort_flag))) { report_ws(a.status, 33); break; }
-            WS_TRACE(2, j, s * 3 + 1);
-            tc_fence_after();
-            issue_pv(s, stv, j > 0);
-            if (j + 1 < nts) {
+            if (!ok) break;
+            if (f & (1u << (2 * s))) {
+              WS_TRACE(2, i, s * 3 + 0);
+              if (!(ok = mbar_wait(&bars[kPFull + s], done[s] & 1u, abort_flag))) { report_ws(a.status, 33); break; }
+              WS_TRACE(2, i, s * 3 + 1);
+              tc_fence_after();
+              issue_pv(s, stv, done[s] > 0);
+              ++done[s];
+            }
+            if (fn & (1u << (2 * s))) {
               if (!k_waited) {
                 if (!(ok = mbar_wait(&bars[kKvFull + stk], (rk / kStages) & 1, abort_flag))) { report_ws(a.status, 34); break; }
                 k_waited = true;
@@ -304,12 +368,12 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
               }
               issue_s(s, stk);
             }
-            WS_TRACE(2, j, s * 3 + 2);
+            WS_TRACE(2, i, s * 3 + 2);
           }
           if (!ok) break;
           if (leader) {
             umma_commit(&bars[kKvEmpty + stv]);
-            if (j + 1 < n_max) umma_commit(&bars[kKvEmpty + stk]);
+            if (i + 1 < n_u) umma_commit(&bars[kKvEmpty + stk]);
           }
         }
       } while (false);
@@ -330,15 +394,20 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t tmem_s = tmem_base + s * kTileN + t_lane;
     const uint32_t tmem_o = tmem_base + 256 + s * 128 + t_lane;
     const float sl2 = a.scale_log2;
-    const int nt = s ? n_tiles[1] : n_tiles[0];
+    const bool active = s ? act[1] : act[0];
+    const uint32_t visit_bit = 1u << (2 * s), mixed_bit = 2u << (2 * s);
     float m_ref = -INFINITY;  // reference maximum the stored P and O are relative to
     float l_run = 0.f;
     bool ok = true;
-    const uint8_t* mrow =
-        (a.mask && nt > 0) ? a.mask + (static_cast<size_t>(b) * a.seq_q + min(r_glob, a.seq_q - 1)) * a.seq_k : nullptr;
+    const uint8_t* mrow = (kMasked && active)
+                              ? a.mask + (static_cast<size_t>(b) * a.seq_q + min(r_glob, a.seq_q - 1)) * a.seq_k
+                              : nullptr;
+    int j = 0;  // key tiles this slot has processed so far
 
-    for (int j = 0; j < nt; ++j) {
-      const int kv0 = j * kTileN;
+    for (int i = 0; i < n_u; ++i) {
+      const uint32_t fl = flag_at(i);
+      if (!(fl & visit_bit)) continue;
+      const int kv0 = tile_at(i) * kTileN;
       WS_TRACE(s, j, 0);
       if (!(ok = mbar_wait(&bars[kSFull + s], j & 1, abort_flag))) { report_ws(a.status, 40); break; }
       WS_TRACE(s, j, 1);
@@ -353,8 +422,8 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
       // ---- masking (tile-uniform decision) ----
       const bool tail = kv0 + kTileN > a.seq_k;
-      const bool diag = a.causal && (kv0 + kTileN - 1 > q0s + off);
-      if (mrow != nullptr) {
+      const bool diag = !kMasked && a.causal && (kv0 + kTileN - 1 > q0s + off);
+      if (kMasked && (fl & mixed_bit)) {
         if (!tail && a.mask_vec) {
           const uint4* mp = reinterpret_cast<const uint4*>(mrow + kv0);
 #pragma unroll
@@ -374,7 +443,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
       } else if (tail || diag) {
-        const int lim = a.causal ? min(a.seq_k - 1, r_glob + off) : a.seq_k - 1;
+        const int lim = (!kMasked && a.causal) ? min(a.seq_k - 1, r_glob + off) : a.seq_k - 1;
 #pragma unroll
         for (int c = 0; c < kTileN; ++c)
           if (kv0 + c > lim) sr[c] = 0xFF800000u;
@@ -444,11 +513,21 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_before();
       mbar_arrive(&bars[kPFull + s]);
       WS_TRACE(s, j, 5);
+      ++j;
     }
+    const int nt = j;
 
     // ---- epilogue: O / l -> out ----
     if (ok && nt > 0) {
       if (!(ok = mbar_wait(&bars[kODone + s], (nt - 1) & 1, abort_flag))) report_ws(a.status, 42);
+    }
+    if (ok && nt == 0 && active && r_glob < a.seq_q) {
+      // no key tile holds a visible key for this slot: the rows are zeros
+      uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) +
+                      2 * (static_cast<size_t>(b) * a.out_stride[0] + static_cast<size_t>(heads) * a.out_stride[1] +
+                           static_cast<size_t>(r_glob) * a.out_stride[2]);
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(0u, 0u, 0u, 0u);
     }
     if (ok && nt > 0) {
       tc_fence_after();
@@ -485,24 +564,24 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool kMasked>
 cudaError_t launch_ws_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillArgs& a,
                           cudaStream_t stream) {
   constexpr int kStages = (D == 128) ? 4 : 8;
-  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 512 + 1024;
+  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 512 + 3 * kMaxList + 1024;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 64 && !attr_done[dev]) {
-    e = cudaFuncSetAttribute(prefill_ws_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(prefill_ws_kernel<D, BF16, kMasked>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
   const int n_qt = (a.seq_q + kTileM - 1) / kTileM;
   dim3 grid = a.pair_heads ? dim3(n_qt, a.n_heads / 2, a.batch) : dim3((n_qt + 1) / 2, a.n_heads, a.batch);
-  prefill_ws_kernel<D, BF16><<<grid, kThreads, smem, stream>>>(tq, tk, tv, a);
+  prefill_ws_kernel<D, BF16, kMasked><<<grid, kThreads, smem, stream>>>(tq, tk, tv, a);
   return cudaGetLastError();
 }
 
@@ -510,9 +589,13 @@ cudaError_t launch_ws_one(const CUtensorMap& tq, const CUtensorMap& tk, const CU
 
 cudaError_t launch_prefill_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                               const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream) {
-  if (head_dim == 128)
-    return bf16 ? launch_ws_one<128, true>(tq, tk, tv, a, stream) : launch_ws_one<128, false>(tq, tk, tv, a, stream);
-  return bf16 ? launch_ws_one<64, true>(tq, tk, tv, a, stream) : launch_ws_one<64, false>(tq, tk, tv, a, stream);
+  const bool masked = a.mask != nullptr;
+  if (head_dim == 128) {
+    if (masked) return bf16 ? launch_ws_one<128, true, true>(tq, tk, tv, a, stream) : launch_ws_one<128, false, true>(tq, tk, tv, a, stream);
+    return bf16 ? launch_ws_one<128, true, false>(tq, tk, tv, a, stream) : launch_ws_one<128, false, false>(tq, tk, tv, a, stream);
+  }
+  if (masked) return bf16 ? launch_ws_one<64, true, true>(tq, tk, tv, a, stream) : launch_ws_one<64, false, true>(tq, tk, tv, a, stream);
+  return bf16 ? launch_ws_one<64, true, false>(tq, tk, tv, a, stream) : launch_ws_one<64, false, false>(tq, tk, tv, a, stream);
 }
 
 }  // namespace minfer_attn

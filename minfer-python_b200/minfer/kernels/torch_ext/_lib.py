@@ -17,6 +17,7 @@ BF16 = 1
 
 EXPORTS = (
     "minfer_attn_prefill",
+    "minfer_attn_prefill_workspace_bytes",
     "minfer_attn_decode",
     "minfer_attn_decode_static",
     "minfer_attn_decode_workspace_bytes",
@@ -48,6 +49,8 @@ class PrefillParams(ctypes.Structure):
         ("causal", ctypes.c_int32),
         ("softmax_scale", ctypes.c_float),
         ("flags", ctypes.c_int32),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
     ]
 
 
@@ -83,6 +86,8 @@ def _load() -> ctypes.CDLL:
     lib = ctypes.CDLL(LIB_PATH)
     lib.minfer_attn_prefill.argtypes = [ctypes.POINTER(PrefillParams), ctypes.c_void_p]
     lib.minfer_attn_prefill.restype = ctypes.c_int
+    lib.minfer_attn_prefill_workspace_bytes.argtypes = [ctypes.c_int32] * 3
+    lib.minfer_attn_prefill_workspace_bytes.restype = ctypes.c_size_t
     lib.minfer_attn_decode.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
     lib.minfer_attn_decode.restype = ctypes.c_int
     lib.minfer_attn_decode_static.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]

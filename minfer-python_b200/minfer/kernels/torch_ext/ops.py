@@ -32,7 +32,8 @@ for _name, _schema in _DEFS.items():
     _library.define(_name + _schema)
 
 _status: dict[int, torch.Tensor] = {}
-_workspace: dict[int, torch.Tensor] = {}
+_workspace: dict[int, torch.Tensor] = {}        # decode split-KV partials, per device
+_mask_workspace: dict[int, torch.Tensor] = {}   # prefill mask tile classes, per device
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -92,6 +93,10 @@ def _prefill(q, k, v, mask, out, causal: bool) -> None:
     p.causal = 1 if causal else 0
     p.softmax_scale = 0.0
     p.flags = 1 if _SIMPLE else 0
+    if mask is not None:
+        need = _lib.lib.minfer_attn_prefill_workspace_bytes(p.batch, p.seq_q, p.seq_k)
+        ws = _workspace_for(q.device, need, _mask_workspace)
+        p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
         _lib.check(_lib.lib.minfer_attn_prefill(ctypes.byref(p), ctypes.c_void_p(stream)), "minfer_attn_prefill")
@@ -115,12 +120,13 @@ def _flash_attn_causal_cuda(q, k, v, out) -> None:
     _prefill(q, k, v, None, out, causal=True)
 
 
-def _decode_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+def _workspace_for(device: torch.device, nbytes: int, cache: dict) -> torch.Tensor:
+    """Per-device scratch owned by this layer (the library itself never allocates); grown on demand."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    t = _workspace.get(idx)
+    t = cache.get(idx)
     if t is None or t.numel() < nbytes:
         t = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspace[idx] = t
+        cache[idx] = t
     return t
 
 
@@ -145,7 +151,7 @@ def _flash_attn_decode_cuda(q, k_cache, v_cache, lens, out) -> None:
     for i in range(3):
         p.kv_stride[i] = k_cache.stride(i)
     need = _lib.lib.minfer_attn_decode_workspace_bytes(p.batch, p.n_heads, p.max_len, p.head_dim, 0)
-    ws = _decode_workspace(q.device, need)
+    ws = _workspace_for(q.device, need, _workspace)
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream

@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     from minfer.kernels.torch_ext import _lib
     for s in declared_symbols():
         assert hasattr(_lib.lib, s), f"{s} declared in the header but not exported"
-    assert _lib.lib.minfer_attn_abi_version() == 1
+    assert _lib.lib.minfer_attn_abi_version() == 2
     assert set(_lib.EXPORTS) <= set(declared_symbols())
 
 
@@ -73,6 +73,18 @@ def test_workspace_size_formula():
     assert L.minfer_attn_decode_workspace_bytes(64, 32, 8192, 128, 0) == 64 * 32 * 16 * 130 * 4
     assert L.minfer_attn_decode_workspace_bytes(64, 32, 8192, 96, 512) == 0
     assert L.minfer_attn_decode_workspace_bytes(1, 1, 1, 64, 64) == 66 * 4
+
+
+def test_prefill_mask_workspace_size():
+    from minfer.kernels.torch_ext import _lib
+    L = _lib.lib
+    assert L.minfer_attn_prefill_workspace_bytes(4, 4096, 4096) == 4 * 32 * 32
+    assert L.minfer_attn_prefill_workspace_bytes(1, 129, 1) == 2
+    assert L.minfer_attn_prefill_workspace_bytes(0, 128, 128) == 0
+    p = _lib.PrefillParams()
+    p.q = p.k = p.v = p.out = p.mask = 0x1000
+    p.batch, p.n_heads, p.n_kv_heads, p.seq_q, p.seq_k, p.head_dim = 1, 2, 2, 128, 128 * 1024 + 1, 128
+    assert L.minfer_attn_prefill(ctypes.byref(p), None) == 2           # masked call beyond 1024 key tiles
 
 
 def test_ops_have_no_cpu_path():

