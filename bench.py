@@ -145,6 +145,11 @@ def cpu_reference_step_inputs(seed: int = 1):
 
 def time_cpu_reference(steps: int, warmup: int):
     from oracle import oracle as O
+    # all host cores this process may use (torchrun pins OMP_NUM_THREADS=1 otherwise)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, OSError):
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     q, k, v, mask = cpu_reference_step_inputs()
     for _ in range(warmup):
         O.sdpa_reference(q, k, v, mask)
@@ -167,7 +172,7 @@ def run_reference_arm(args):
               "with expanded K/V and a dense causal mask")
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * PREFILL["batch"],
+        "steps": min(args.steps, 20), "warmup": min(max(args.warmup, 1), 3), "ms_per_step": sec * 1e3 * PREFILL["batch"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "l2": "n/a (CPU)"},
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},

@@ -54,7 +54,9 @@ def flash_attn_causal(kerns, args, dtype):
 def flash_attn_decode(kerns, args, dtype):
     B, H, Hkv, D, Lmax = args.batch, args.heads, args.kv_heads, args.head_dim, args.seq
     g = torch.Generator().manual_seed(args.seed)
-    lens = torch.randint(max(1, Lmax // 16), Lmax + 1, (B,), generator=g, dtype=torch.int32).cuda()
+    lens = torch.randint(max(1, Lmax // 16), Lmax + 1, (B,), generator=g, dtype=torch.int32)
+    print(f"decode: sum(lens) = {int(lens.sum())}, live KV bytes = {int(lens.sum()) * Hkv * D * 2 * 2}")
+    lens = lens.cuda()
     q = torch.randn((B, H, 1, D), dtype=dtype, device="cuda")
     kc = torch.randn((B, Hkv, Lmax, D), dtype=dtype, device="cuda")
     vc = torch.randn((B, Hkv, Lmax, D), dtype=dtype, device="cuda")
