@@ -40,6 +40,10 @@ extern "C" {
  * two-tile warp-specialised one.  Same results within tolerance; kept for
  * cross-checking. */
 #define MINFER_ATTN_FLAG_SIMPLE_KERNEL 1
+/* Run the two-tile kernel with one work item per thread block instead of the
+ * persistent form (one block per SM walking a list of items).  Dense-mask calls
+ * always run this way.  Kept for cross-checking. */
+#define MINFER_ATTN_FLAG_ONE_ITEM_PER_CTA 2
 
 /* error codes */
 #define MINFER_ATTN_OK            0

@@ -178,9 +178,12 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
   a.scale_log2 = scale * 1.4426950408889634f;
 
   a.pair_heads = (a.group % 2 == 0) ? 1 : 0;
-  cudaError_t e = (p->flags & MINFER_ATTN_FLAG_SIMPLE_KERNEL)
-                      ? launch_prefill(tq, tk, tv, a, p->head_dim, bf16, static_cast<cudaStream_t>(stream))
-                      : launch_prefill_ws(tq, tk, tv, a, p->head_dim, bf16, static_cast<cudaStream_t>(stream));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (p->flags & MINFER_ATTN_FLAG_SIMPLE_KERNEL) e = launch_prefill(tq, tk, tv, a, p->head_dim, bf16, st);
+  else if (a.mask != nullptr || (p->flags & MINFER_ATTN_FLAG_ONE_ITEM_PER_CTA))
+    e = launch_prefill_ws(tq, tk, tv, a, p->head_dim, bf16, st);
+  else e = launch_prefill_persist(tq, tk, tv, a, p->head_dim, bf16, st);
   return cuda_result(e);
 }
 

@@ -23,6 +23,7 @@ struct PrefillArgs {
   int32_t causal;
   int32_t mask_vec;       // mask rows may be read with 16-byte loads
   int32_t pair_heads;     // two-tile kernel: slots are two heads of one kv head (else two row tiles)
+  int32_t items_x, items_y;  // persistent kernel: work-item grid (query tile [pairs], head [pairs]); set by its launcher
   float scale_log2;       // softmax scale * log2(e)
   // position (1..3) of the batch / head / row coordinate inside each tensor
   // map; coordinate 0 is always head_dim
@@ -33,6 +34,8 @@ struct PrefillArgs {
 size_t prefill_smem_bytes(int head_dim);
 cudaError_t launch_prefill_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                               const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream);
+cudaError_t launch_prefill_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                                   const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream);
 cudaError_t launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillArgs& a,
                            int head_dim, bool bf16, cudaStream_t stream);
 

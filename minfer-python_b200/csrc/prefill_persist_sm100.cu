@@ -1,0 +1,521 @@
+// Persistent form of the two-tile prefill kernel for causal / unmasked calls.
+//
+// Same roles, tensor-memory layout and MMA issue order as prefill_ws_sm100.cu
+// (which remains the kernel for dense masks), but one CTA per SM walks a list of
+// work items instead of exiting after one.  What that buys: tensor memory and the
+// barriers are set up once; the TMA warp already streams the next item's Q/K/V
+// while the softmax warps write the previous item's output; and the MMA warp
+// starts the next item's first score tiles as soon as its operands have landed,
+// so the ~3k-cycle prologue and most of the epilogue of an item disappear from
+// the critical path.
+//
+// Fills the launch the reference leaves unimplemented
+// (src/minfer/kernels/torch_ext/csrc/cuda/flash_attn/op.cuh:105; empty kernel at
+// .../flash_attn/kernels/kernel.cuh:16-27).
+//
+// Work items are (query tile or tile pair, head pair or head, batch) ordered by
+// decreasing number of key tiles; CTA c takes items c, 2G-1-c, 2G+c, ... (a snake
+// over rounds of G = gridDim.x items) so every CTA gets the same mix of long and
+// short items without a global counter.
+//
+// Hand-offs between items, per slot s (all counted over the CTA's lifetime, so
+// mbarrier parities keep alternating):
+//   q_empty[s]  MMA -> TMA      last S MMA of the item has read Q_s
+//   o_free[s]   softmax -> MMA  the epilogue has copied O_s out of tensor memory
+// The K/V ring simply continues across items.
+#include "attn_internal.h"
+#include "ptx.cuh"
+
+namespace minfer_attn {
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 128;
+constexpr int kBlockBytes = 128 * 128;
+constexpr int kThreads = 384;  // softmax 0 (warps 0-3), softmax 1 (4-7), MMA (8), TMA (9), 2 idle warps
+// setmaxnreg split of the 384 x 168 launch allocation: 8 x 216 + 4 x 72 = 12 x 168
+constexpr int kRegsSoftmax = 216;
+constexpr int kRegsOther = 72;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef MINFER_ATTN_POLY_OF_8
+#define MINFER_ATTN_POLY_OF_8 2
+#endif
+constexpr int kPolyOf8 = MINFER_ATTN_POLY_OF_8;  // share of exp2 evaluations done without the SFU
+
+// barrier indices ([2] = one per slot)
+constexpr int kQFull = 0;
+constexpr int kQEmpty = 2;
+constexpr int kSFull = 4;
+constexpr int kPFull = 6;
+constexpr int kODone = 8;
+constexpr int kOFree = 10;
+constexpr int kKvFull = 12;  // [kStages], then kKvEmpty [kStages]
+
+__device__ __forceinline__ void report_p(int32_t* status, int site) {
+  if (status != nullptr && atomicCAS(status, 0, kStatusWaitTimeout) == 0) {
+    status[1] = static_cast<int32_t>(blockIdx.x);
+    status[2] = 0;
+    status[3] = site;
+  }
+}
+
+// One work item: the two slots' heads, first query rows and key-tile counts.
+struct Item {
+  int b, kvh;
+  int head[2], q0[2], n[2];
+};
+
+__device__ __forceinline__ Item decode_item(const PrefillArgs& a, int id) {
+  // id runs over [0, n_x * n_y * batch), long (late) query tiles first
+  Item it;
+  const int per_x = a.items_y * a.batch;
+  const int xr = a.items_x - 1 - id / per_x;
+  const int rem = id % per_x;
+  const int y = rem % a.items_y;
+  it.b = rem / a.items_y;
+  if (a.pair_heads) {
+    it.head[0] = 2 * y;
+    it.head[1] = 2 * y + 1;
+    it.q0[0] = it.q0[1] = xr * kTileM;
+  } else {
+    it.head[0] = it.head[1] = y;
+    it.q0[0] = 2 * xr * kTileM;
+    it.q0[1] = it.q0[0] + kTileM;
+  }
+  it.kvh = it.head[0] / a.group;
+  const int n_all = (a.seq_k + kTileN - 1) / kTileN;
+  const int off = a.seq_k - a.seq_q;
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    if (it.q0[s] >= a.seq_q) {
+      it.n[s] = 0;
+    } else if (a.causal) {
+      const int last_row = min(it.q0[s] + kTileM - 1, a.seq_q - 1);
+      it.n[s] = min(n_all, (last_row + off) / kTileN + 1);
+    } else {
+      it.n[s] = n_all;
+    }
+  }
+  return it;
+}
+
+// k-th item of this CTA (snake over rounds), or -1 past the end
+__device__ __forceinline__ int item_id(int k, int n_items) {
+  const int g = gridDim.x;
+  const int c = (k & 1) ? (g - 1 - static_cast<int>(blockIdx.x)) : static_cast<int>(blockIdx.x);
+  const int id = k * g + c;
+  return id < n_items ? id : -1;
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, const PrefillArgs a) {
+  constexpr int kDB = D / 64;
+  constexpr int kTileBytes = kDB * kBlockBytes;
+  constexpr int kStages = (D == 128) ? 4 : 8;
+  constexpr int kKvEmpty = kKvFull + kStages;
+  constexpr int kNumBars = kKvFull + 2 * kStages;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kIdescS = umma_idesc(kTileM, kTileN, BF16, false, false);
+  constexpr uint32_t kIdescO = umma_idesc(kTileM, D, BF16, false, true);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* s_q = smem;                   // [2][kTileBytes]
+  uint8_t* s_kv = s_q + 2 * kTileBytes;  // [kStages][kTileBytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_kv + kStages * kTileBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int n_items = a.items_x * a.items_y * a.batch;
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[kQFull + i], 1);
+      mbar_init(&bars[kQEmpty + i], 1);
+      mbar_init(&bars[kSFull + i], 1);
+      mbar_init(&bars[kPFull + i], 128);
+      mbar_init(&bars[kODone + i], 1);
+      mbar_init(&bars[kOFree + i], 128);
+    }
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&bars[kKvFull + i], 1);
+      mbar_init(&bars[kKvEmpty + i], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+    if (warp == 9) {
+      // ==================================================================
+      // TMA producer (converged warp, one elected lane issues)
+      // ==================================================================
+      const bool leader = elect_one() != 0;
+      if (leader) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+      }
+      auto pick = [](int i, const int32_t* pos, int vb, int vh, int vr) {
+        return pos[0] == i ? vb : (pos[1] == i ? vh : vr);
+      };
+      auto load_tile = [&](const CUtensorMap* tm, uint32_t dst, uint64_t* bar, const int32_t* pos, int bb, int hh,
+                           int row) {
+        const int c1 = pick(1, pos, bb, hh, row), c2 = pick(2, pos, bb, hh, row), c3 = pick(3, pos, bb, hh, row);
+        if (leader) {
+          mbar_arrive_expect_tx(bar, kTileBytes);
+#pragma unroll
+          for (int db = 0; db < kDB; ++db) tma_load_4d_addr(dst + db * kBlockBytes, tm, bar, db * 64, c1, c2, c3);
+        }
+      };
+      const uint32_t q_addr = smem_u32(s_q), kv_addr = smem_u32(s_kv);
+      bool ok = true;
+      uint32_t q_loads[2] = {0u, 0u};  // Q tiles loaded so far per slot
+      uint32_t r = 0;                  // K/V ring position over the CTA's lifetime
+      for (int k = 0; ok; ++k) {
+        const int id = item_id(k, n_items);
+        if (id < 0) break;
+        const Item it = decode_item(a, id);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (it.n[s] == 0 || !ok) continue;
+          if (q_loads[s] > 0 &&
+              !(ok = mbar_wait(&bars[kQEmpty + s], (q_loads[s] - 1) & 1u, abort_flag))) {
+            report_p(a.status, 21);
+            continue;
+          }
+          load_tile(&tm_q, q_addr + s * kTileBytes, &bars[kQFull + s], a.q_pos, it.b, it.head[s], it.q0[s]);
+          ++q_loads[s];
+        }
+        const int n_loads = 2 * max(it.n[0], it.n[1]);  // K0 V0 K1 V1 ...
+        for (int t = 0; t < n_loads && ok; ++t, ++r) {
+          const uint32_t st = r % kStages;
+          if (r >= kStages && !(ok = mbar_wait(&bars[kKvEmpty + st], ((r / kStages) - 1) & 1u, abort_flag))) {
+            report_p(a.status, 20);
+            break;
+          }
+          load_tile((t & 1) ? &tm_v : &tm_k, kv_addr + st * kTileBytes, &bars[kKvFull + st], a.kv_pos, it.b, it.kvh,
+                    (t >> 1) * kTileN);
+        }
+      }
+      if (!ok || *abort_flag) {
+        // the CTA is giving up: let the copies already issued land before the
+        // shared memory is handed back (bounded polls)
+        for (int i = 0; i < 4000000; ++i) {
+          bool pending = false;
+#pragma unroll
+          for (int s = 0; s < 2; ++s)
+            if (q_loads[s] > 0) pending |= !mbar_try_wait(&bars[kQFull + s], (q_loads[s] - 1) & 1u);
+          const uint32_t lo = r > static_cast<uint32_t>(kStages) ? r - kStages : 0u;
+          for (uint32_t x = lo; x < r; ++x) pending |= !mbar_try_wait(&bars[kKvFull + x % kStages], (x / kStages) & 1u);
+          if (!pending) break;
+        }
+      }
+      __syncwarp();
+    } else if (warp == 8) {
+      // ==================================================================
+      // MMA issuer (converged warp, one elected lane issues; descriptors are
+      // (hi, lo) pairs of which only the start address in `lo` changes)
+      // ==================================================================
+      const bool leader = elect_one() != 0;
+      bool ok = true;
+      constexpr uint32_t kHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+      constexpr uint32_t kLoK = (16u >> 4) << 16;
+      constexpr uint32_t kLoV = (static_cast<uint32_t>(kBlockBytes) >> 4) << 16;  // LBO = one block for MN-major V
+      const uint32_t q_lo = (smem_u32(s_q) >> 4) | kLoK;
+      const uint32_t k_lo = (smem_u32(s_kv) >> 4) | kLoK;
+      const uint32_t v_lo = (smem_u32(s_kv) >> 4) | kLoV;
+      auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+
+      auto issue_s = [&](int s, uint32_t st) {
+        const uint32_t qa = q_lo + s * (kTileBytes >> 4);
+        const uint32_t ka = k_lo + st * (kTileBytes >> 4);
+        const uint32_t ts = tmem_base + s * kTileN;
+#pragma unroll
+        for (int i = 0; i < kDB * 4; ++i) {
+          const uint32_t o = (i >> 2) * (kBlockBytes >> 4) + (i & 3) * 2;  // 32 bytes per 16-element k step
+          if (leader) {
+            if (i == 0) umma_ss_first(ts, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
+            else umma_ss_acc(ts, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
+          }
+        }
+        if (leader) umma_commit(&bars[kSFull + s]);
+      };
+      auto issue_pv = [&](int s, uint32_t st, bool accumulate) {
+        const uint32_t va = v_lo + st * (kTileBytes >> 4);
+        const uint32_t tp = tmem_base + s * kTileN;  // P: packed 16-bit pairs, 8 columns per 16 keys
+        const uint32_t to = tmem_base + 256 + s * 128;
+        if (leader) umma_ts(to, tp, desc(va, kHi), kIdescO, accumulate ? 1u : 0u);
+#pragma unroll
+        for (int kk = 1; kk < kTileN / 16; ++kk)
+          if (leader) umma_ts_acc(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO);
+        if (leader) umma_commit(&bars[kODone + s]);
+      };
+
+      uint32_t tiles[2] = {0u, 0u};  // key tiles finished per slot (parity of p_full)
+      uint32_t items[2] = {0u, 0u};  // items started per slot (parity of q_full / o_free)
+      uint32_t r = 0;                // K/V ring position, in step with the TMA warp
+      for (int k = 0; ok; ++k) {
+        const int id = item_id(k, n_items);
+        if (id < 0) break;
+        const Item it = decode_item(a, id);
+        const int n_max = max(it.n[0], it.n[1]);
+        if (n_max == 0) continue;
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (it.n[s] > 0 && ok && !(ok = mbar_wait(&bars[kQFull + s], items[s] & 1u, abort_flag)))
+            report_p(a.status, 30);
+        }
+        if (!ok) break;
+        // first K tile of the item
+        if (!(ok = mbar_wait(&bars[kKvFull + r % kStages], (r / kStages) & 1u, abort_flag))) { report_p(a.status, 31); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (it.n[s] > 0) {
+            issue_s(s, r % kStages);
+            if (it.n[s] == 1 && leader) umma_commit(&bars[kQEmpty + s]);  // that was the slot's last S of the item
+          }
+        }
+        if (leader) umma_commit(&bars[kKvEmpty + r % kStages]);
+
+        for (int j = 0; j < n_max && ok; ++j) {
+          const uint32_t rv = r + 2 * j + 1;  // ring position of V_j
+          const uint32_t rk = r + 2 * j + 2;  // ring position of K_{j+1}
+          const uint32_t stv = rv % kStages, stk = rk % kStages;
+          if (!(ok = mbar_wait(&bars[kKvFull + stv], (rv / kStages) & 1u, abort_flag))) { report_p(a.status, 32); break; }
+          bool k_waited = false;
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            if (!ok || j >= it.n[s]) continue;
+            if (j == 0 && items[s] > 0) {
+              // O_s still holds the previous item's result until its epilogue has read it
+              if (!(ok = mbar_wait(&bars[kOFree + s], (items[s] - 1) & 1u, abort_flag))) { report_p(a.status, 35); continue; }
+            }
+            if (!(ok = mbar_wait(&bars[kPFull + s], tiles[s] & 1u, abort_flag))) { report_p(a.status, 33); continue; }
+            tc_fence_after();
+            issue_pv(s, stv, j > 0);
+            ++tiles[s];
+            if (j + 1 < it.n[s]) {
+              if (!k_waited) {
+                if (!(ok = mbar_wait(&bars[kKvFull + stk], (rk / kStages) & 1u, abort_flag))) { report_p(a.status, 34); continue; }
+                k_waited = true;
+                tc_fence_after();
+              }
+              issue_s(s, stk);
+              if (j + 2 == it.n[s] && leader) umma_commit(&bars[kQEmpty + s]);  // last S of the item for this slot
+            }
+          }
+          if (!ok) break;
+          if (leader) {
+            umma_commit(&bars[kKvEmpty + stv]);
+            if (j + 1 < n_max) umma_commit(&bars[kKvEmpty + stk]);
+          }
+        }
+        r += 2 * n_max;
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+          if (it.n[s] > 0) ++items[s];
+      }
+      __syncwarp();
+    }
+  } else {
+    // ====================================================================
+    // softmax (+ lazy correction + epilogue) of slot s
+    // ====================================================================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+    const int s = warp >> 2;
+    const int row = tid & 127;
+    const uint32_t t_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + s * kTileN + t_lane;
+    const uint32_t tmem_o = tmem_base + 256 + s * 128 + t_lane;
+    const float sl2 = a.scale_log2;
+    const int off = a.seq_k - a.seq_q;
+    bool ok = true;
+    uint32_t jt = 0;  // key tiles this slot has processed over the CTA's lifetime
+
+    for (int k = 0; ok; ++k) {
+      const int id = item_id(k, n_items);
+      if (id < 0) break;
+      const Item it = decode_item(a, id);
+      const int nt = s ? it.n[1] : it.n[0];
+      if (nt == 0) continue;
+      const int q0s = s ? it.q0[1] : it.q0[0];
+      const int heads = s ? it.head[1] : it.head[0];
+      const int r_glob = q0s + row;
+      float m_ref = -INFINITY;  // reference maximum the stored P and O are relative to
+      float l_run = 0.f;
+
+      for (int j = 0; j < nt; ++j, ++jt) {
+        const int kv0 = j * kTileN;
+        if (!(ok = mbar_wait(&bars[kSFull + s], jt & 1u, abort_flag))) { report_p(a.status, 40); break; }
+        tc_fence_after();
+
+        uint32_t sr[kTileN];
+#pragma unroll
+        for (int c = 0; c < kTileN / 32; ++c)
+          tmem_ld32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
+        tc_wait_ld();
+
+        // ---- masking: only the diagonal and the ragged last tile need it ----
+        const bool tail = kv0 + kTileN > a.seq_k;
+        const bool diag = a.causal && (kv0 + kTileN - 1 > q0s + off);
+        if (tail || diag) {
+          const int lim = a.causal ? min(a.seq_k - 1, r_glob + off) : a.seq_k - 1;
+#pragma unroll
+          for (int c = 0; c < kTileN; ++c)
+            if (kv0 + c > lim) sr[c] = 0xFF800000u;
+        }
+
+        // ---- row maximum; move the reference only when it lags by > 2^8 ----
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < kTileN; c += 8) {
+          mx0 = fmax3(mx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+          mx2 = fmax3(mx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
+          mx3 = fmax3(mx3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        const bool move = (mx != -INFINITY) && (m_ref == -INFINITY || (mx - m_ref) * sl2 > kRescaleThreshold);
+        if (__any_sync(0xFFFFFFFFu, move)) {
+          const float alpha = (move && m_ref != -INFINITY) ? ex2_approx((m_ref - mx) * sl2) : 1.f;
+          if (move) m_ref = mx;
+          l_run *= alpha;
+          if (j > 0) {
+            // PV(j-1) of this slot must have landed before O is touched
+            if (!(ok = mbar_wait(&bars[kODone + s], (jt - 1) & 1u, abort_flag))) { report_p(a.status, 41); break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tmem_o + c * 32, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+              tmem_st32(tmem_o + c * 32, o);
+            }
+          }
+        }
+
+        // ---- P = exp2(S*c - m*c) -> 16-bit pairs -> tensor memory (over S) ----
+        const float mb = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
+        const float2 sl2_2 = make_float2(sl2, sl2);
+        const float2 nmb_2 = make_float2(-mb, -mb);
+        float2 sum2 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < kTileN / 32; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float2 sp = make_float2(__uint_as_float(sr[c * 32 + 2 * e]), __uint_as_float(sr[c * 32 + 2 * e + 1]));
+            const float2 x = __ffma2_rn(sp, sl2_2, nmb_2);
+            float2 p;
+            // kPolyOf8 of every 8 pairs go through the FMA-pipe polynomial, the rest
+            // through the special-function unit, so both units stay busy
+            if ((e & 7) < kPolyOf8) {
+              p = ex2_poly2(x);
+            } else {
+              p.x = ex2_approx(x.x);
+              p.y = ex2_approx(x.y);
+            }
+            sum2 = __fadd2_rn(sum2, p);
+            pk[e] = pack2<BF16>(p.x, p.y);
+          }
+          tmem_st16(tmem_s + c * 16, pk);
+        }
+        l_run += sum2.x + sum2.y;
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars[kPFull + s]);
+      }
+      if (!ok) break;
+
+      // ---- epilogue: copy O out of tensor memory, release it, then write O / l ----
+      if (!(ok = mbar_wait(&bars[kODone + s], (jt - 1) & 1u, abort_flag))) { report_p(a.status, 42); break; }
+      tc_fence_after();
+      const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
+      uint32_t ow[D / 2];  // the row as packed 16-bit pairs
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tmem_o + c * 32, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+          ow[c * 16 + e] = pack2<BF16>(__uint_as_float(o[2 * e]) * inv, __uint_as_float(o[2 * e + 1]) * inv);
+      }
+      tc_fence_before();
+      mbar_arrive(&bars[kOFree + s]);  // the MMA warp may overwrite O_s for the next item
+      if (r_glob < a.seq_q) {
+        uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) +
+                        2 * (static_cast<size_t>(it.b) * a.out_stride[0] + static_cast<size_t>(heads) * a.out_stride[1] +
+                             static_cast<size_t>(r_glob) * a.out_stride[2]);
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c)
+          *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(ow[c * 4], ow[c * 4 + 1], ow[c * 4 + 2], ow[c * 4 + 3]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int D, bool BF16>
+cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, PrefillArgs a,
+                               cudaStream_t stream) {
+  constexpr int kStages = (D == 128) ? 4 : 8;
+  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 512 + 1024;
+  static bool attr_done[64] = {};
+  static int sm_count[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_done[dev]) {
+    e = cudaFuncSetAttribute(prefill_persist_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    attr_done[dev] = true;
+  }
+  const int n_qt = (a.seq_q + kTileM - 1) / kTileM;
+  a.items_x = a.pair_heads ? n_qt : (n_qt + 1) / 2;
+  a.items_y = a.pair_heads ? a.n_heads / 2 : a.n_heads;
+  const long long n_items = static_cast<long long>(a.items_x) * a.items_y * a.batch;
+  if (n_items > 0x7FFFFFFF) return cudaErrorInvalidValue;
+  const int grid = static_cast<int>(n_items < sm_count[dev] ? n_items : sm_count[dev]);
+  prefill_persist_kernel<D, BF16><<<grid, kThreads, smem, stream>>>(tq, tk, tv, a);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_prefill_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                                   const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream) {
+  if (head_dim == 128)
+    return bf16 ? launch_persist_one<128, true>(tq, tk, tv, a, stream) : launch_persist_one<128, false>(tq, tk, tv, a, stream);
+  return bf16 ? launch_persist_one<64, true>(tq, tk, tv, a, stream) : launch_persist_one<64, false>(tq, tk, tv, a, stream);
+}
+
+}  // namespace minfer_attn

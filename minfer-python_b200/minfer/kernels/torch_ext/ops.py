@@ -20,6 +20,7 @@ from . import _lib
 _DEBUG = os.environ.get("MINFER_ATTN_DEBUG", "0") not in ("", "0")
 # cross-check aid: run the single-tile prefill kernel instead of the two-tile one
 _SIMPLE = os.environ.get("MINFER_ATTN_SIMPLE_KERNEL", "0") not in ("", "0")
+_FLAGS = int(os.environ.get("MINFER_ATTN_FLAGS", "0"))  # extra MINFER_ATTN_FLAG_* bits, for cross-checking
 
 _DEFS = {
     "flash_attn": "(int qtype_int, int qblock_size, int qtype_size, Tensor q, Tensor k, Tensor v, "
@@ -92,7 +93,7 @@ def _prefill(q, k, v, mask, out, causal: bool) -> None:
     p.dtype = _dtype_tag(q)
     p.causal = 1 if causal else 0
     p.softmax_scale = 0.0
-    p.flags = 1 if _SIMPLE else 0
+    p.flags = (1 if _SIMPLE else 0) | _FLAGS
     if mask is not None:
         need = _lib.lib.minfer_attn_prefill_workspace_bytes(p.batch, p.seq_q, p.seq_k)
         ws = _workspace_for(q.device, need, _mask_workspace)
