@@ -191,6 +191,51 @@ int32_t minfer_attn_decode_default_chunk(int32_t batch, int32_t n_kv_heads,
 #define MINFER_ATTN_STATIC_SCRATCH_BYTES (32u << 20)
 int minfer_attn_decode_static(const MinferAttnDecodeParams* params, void* stream);
 
+/*
+ * Rotary position embedding of q and k fused with the KV-cache append (the step
+ * right before attention).  Reference semantics: il_rope / neox_rope,
+ *   src/minfer/kernels/torch_ext/csrc/cuda/il_rope/op.cuh:21-59, kernel.cuh:9-39
+ *   src/minfer/kernels/torch_ext/csrc/cuda/neox_rope/kernel.cuh:9-38
+ * (one [B, L, H, D] tensor rotated in place per call); the cache layout
+ * [batch, n_kv_heads, max_len, head_dim] is the one src/minfer/core.py:105-127
+ * allocates.  The reference has no fused append.
+ *
+ * q [batch, seq, n_heads, head_dim] is rotated in place.  k, v
+ * [batch, seq, n_kv_heads, head_dim]: with caches given, rotated k and plain v of
+ * token l of sequence b are written to cache row start[b] + l (start: device
+ * int32[batch], or NULL for the scalar start_pos); without caches k is rotated
+ * in place and v is not touched.  Any of q / k / v may be NULL.  Strides are in
+ * elements (batch, token, head for q/k/v; batch, head, row for the caches),
+ * innermost stride 1, multiples of 8; pointers 16-byte aligned.  rotary_dim is
+ * a multiple of 8 (16 for the neox style) and at most head_dim; head_dim is a
+ * multiple of 8.  style: 0 = interleaved pairs, 1 = neox (two halves).
+ * The caller guarantees start[b] + seq <= max_len.
+ */
+typedef struct MinferRopeParams {
+  void*          q;
+  const void*    k;
+  const void*    v;
+  void*          k_cache;
+  void*          v_cache;
+  const int32_t* start;
+  int64_t q_stride[3];
+  int64_t kv_stride[3];
+  int64_t cache_stride[3];
+  int32_t batch;
+  int32_t seq;
+  int32_t n_heads;
+  int32_t n_kv_heads;
+  int32_t head_dim;
+  int32_t rotary_dim;
+  int32_t start_pos;
+  int32_t max_len;
+  int32_t dtype;
+  int32_t style;
+  float   freq_base;
+} MinferRopeParams;
+
+int minfer_attn_rope_append(const MinferRopeParams* params, void* stream);
+
 const char* minfer_attn_strerror(int code);
 /* Text of the CUDA error behind the calling thread's latest MINFER_ATTN_ECUDA
  * from a launch ("no error" if none). */

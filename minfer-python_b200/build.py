@@ -20,7 +20,7 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OUT_DIR = os.path.join(HERE, "minfer", "kernels", "torch_ext")
 LIB_NAME = "libminfer_attn.so"
-SOURCES = ["attn_api.cu", "prefill_sm100.cu", "prefill_ws_sm100.cu", "prefill_persist_sm100.cu", "mask_classify.cu", "decode_sm100.cu", "decode_static_sm100.cu"]
+SOURCES = ["attn_api.cu", "prefill_sm100.cu", "prefill_ws_sm100.cu", "prefill_persist_sm100.cu", "mask_classify.cu", "decode_sm100.cu", "decode_static_sm100.cu", "rope_append_sm100.cu"]
 HEADERS = ["attn_internal.h", "ptx.cuh"]
 
 NVCC_FLAGS = [

@@ -192,6 +192,52 @@ size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t
   return static_cast<size_t>(batch) * ((seq_q + 127) / 128) * ((seq_k + 127) / 128);
 }
 
+int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {
+  if (p == nullptr) return MINFER_ATTN_EINVAL;
+  if (p->q == nullptr && p->k == nullptr && p->v == nullptr) return MINFER_ATTN_EINVAL;
+  if (p->batch <= 0 || p->seq <= 0 || p->head_dim <= 0 || p->head_dim % 8 != 0) return MINFER_ATTN_EINVAL;
+  if (p->dtype != MINFER_ATTN_F16 && p->dtype != MINFER_ATTN_BF16) return MINFER_ATTN_EINVAL;
+  if (p->style != 0 && p->style != 1) return MINFER_ATTN_EINVAL;
+  if (p->rotary_dim < 0 || p->rotary_dim > p->head_dim || p->rotary_dim % (p->style == 1 ? 16 : 8) != 0)
+    return MINFER_ATTN_EINVAL;
+  if (!(p->freq_base > 0.f)) return MINFER_ATTN_EINVAL;
+  if (p->q != nullptr && (p->n_heads <= 0 || !aligned16(p->q) || !strides_ok(p->q_stride, 3))) return MINFER_ATTN_EINVAL;
+  if ((p->k != nullptr || p->v != nullptr) && (p->n_kv_heads <= 0 || !strides_ok(p->kv_stride, 3)))
+    return MINFER_ATTN_EINVAL;
+  if ((p->k != nullptr && !aligned16(p->k)) || (p->v != nullptr && !aligned16(p->v))) return MINFER_ATTN_EINVAL;
+  if ((p->k_cache == nullptr) != (p->v_cache == nullptr)) return MINFER_ATTN_EINVAL;
+  if (p->k_cache != nullptr) {
+    if (p->k == nullptr || p->v == nullptr) return MINFER_ATTN_EINVAL;
+    if (!aligned16(p->k_cache) || !aligned16(p->v_cache) || !strides_ok(p->cache_stride, 3)) return MINFER_ATTN_EINVAL;
+    if (p->max_len <= 0) return MINFER_ATTN_EINVAL;
+    if (p->start == nullptr && (p->start_pos < 0 || p->start_pos + p->seq > p->max_len)) return MINFER_ATTN_EINVAL;
+  }
+  if (p->start == nullptr && p->start_pos < 0) return MINFER_ATTN_EINVAL;
+  int rc = check_device();
+  if (rc != MINFER_ATTN_OK) return rc;
+  RopeArgs a{};
+  a.q = p->q;
+  a.k = p->k;
+  a.v = p->v;
+  a.k_cache = p->k_cache;
+  a.v_cache = p->v_cache;
+  a.start = p->start;
+  for (int i = 0; i < 3; ++i) {
+    a.q_stride[i] = p->q_stride[i];
+    a.kv_stride[i] = p->kv_stride[i];
+    a.cache_stride[i] = p->cache_stride[i];
+  }
+  a.batch = p->batch;
+  a.seq = p->seq;
+  a.n_heads = p->n_heads;
+  a.n_kv_heads = p->n_kv_heads;
+  a.head_dim = p->head_dim;
+  a.rotary_dim = p->rotary_dim;
+  a.start_pos = p->start_pos;
+  a.freq_base = p->freq_base;
+  return cuda_result(launch_rope_append(a, p->dtype == MINFER_ATTN_BF16, p->style == 1, static_cast<cudaStream_t>(stream)));
+}
+
 int32_t minfer_attn_decode_default_chunk(int32_t batch, int32_t n_kv_heads, int32_t max_len) {
   if (batch <= 0 || n_kv_heads <= 0 || max_len <= 0) return 0;
   return default_chunk(batch, n_kv_heads, max_len);

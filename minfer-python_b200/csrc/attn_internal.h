@@ -44,6 +44,22 @@ cudaError_t launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const C
 cudaError_t launch_mask_classify(const uint8_t* mask, uint8_t* cls, int batch, int seq_q, int seq_k,
                                  cudaStream_t stream);
 
+// Kernel-side view of a RoPE + KV-append call.  Strides in elements.
+struct RopeArgs {
+  void* q;              // [batch, seq, n_heads, head_dim], rotated in place; may be null
+  const void* k;        // [batch, seq, n_kv_heads, head_dim]; may be null
+  const void* v;        // same shape as k; may be null
+  void* k_cache;        // [batch, n_kv_heads, max_len, head_dim]; null: rotate k in place
+  void* v_cache;
+  const int32_t* start; // device [batch] first position per sequence, or null: start_pos
+  int64_t q_stride[3];      // batch, token, head
+  int64_t kv_stride[3];     // batch, token, head
+  int64_t cache_stride[3];  // batch, head, row
+  int32_t batch, seq, n_heads, n_kv_heads, head_dim, rotary_dim, start_pos;
+  float freq_base;
+};
+cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, bool neox, cudaStream_t stream);
+
 // Kernel-side view of a decode call.
 struct DecodeArgs {
   const void* q;

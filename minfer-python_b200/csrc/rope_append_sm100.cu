@@ -1,0 +1,186 @@
+// Rotary position embedding of q and k fused with the KV-cache append: the step
+// immediately before attention.  HBM-bound and elementwise.
+//
+// Semantics follow the reference's RoPE ops
+// (src/minfer/kernels/torch_ext/csrc/cuda/il_rope/kernel.cuh:9-39 and
+// .../neox_rope/kernel.cuh:9-38; oracles src/minfer/kernels/refs.py:12-47):
+//   freq_i  = freq_base ^ (-2 i / rotary_dim)            (fp32)
+//   angle   = (position) * freq_i                        (fp32)
+//   interleaved: (x[2i], x[2i+1])            rotated by angle_i
+//   neox:        (x[i],  x[i + rotary_dim/2]) rotated by angle_i
+// for i < rotary_dim/2, elements beyond rotary_dim untouched, math in fp32,
+// result rounded to the 16-bit type.  The reference rotates one [B, L, H, D]
+// tensor in place per call; here one launch rotates q in place, rotates k into
+// the cache [B, Hkv, Lmax, D] at row position and copies v into its cache, so
+// q, k and v are each read once and the [B, L, H, D] -> [B, H, L, D] transposition
+// of k/v costs nothing extra (the cache layout is the reference's,
+// src/minfer/core.py:105-127).
+//
+// Thread mapping: a thread owns one token and one 16-byte chunk of head_dim
+// (neox: the chunk and its partner chunk) and loops over all heads, so the
+// sin/cos of its 4 (8) angles are computed once per token, not once per head.
+#include "../../include/minfer_attn.h"
+#include "attn_internal.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace minfer_attn {
+
+namespace {
+
+template <bool BF16>
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (BF16) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    } else {
+      const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      const float2 t = __half22float2(h);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (BF16) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+      const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// kNeox = false: interleaved pairs; true: two halves.
+template <bool BF16, bool kNeox>
+__global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
+  const int chunks = a.head_dim / 8;                 // 16-byte chunks per head row
+  const int rot_chunks = a.rotary_dim / 8;
+  const int work_chunks = kNeox ? chunks - rot_chunks / 2 : chunks;  // neox: a thread takes a chunk and its partner
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long token = gid / work_chunks;
+  if (token >= static_cast<long long>(a.batch) * a.seq) return;
+  int c = static_cast<int>(gid % work_chunks);
+  // neox work item c: c < rot_chunks/2 -> rotated pair (c, c + rot_chunks/2); else passthrough chunk c + rot_chunks/2
+  int c2 = -1;
+  bool rotate;
+  if (kNeox) {
+    if (c < rot_chunks / 2) {
+      c2 = c + rot_chunks / 2;
+      rotate = true;
+    } else {
+      c += rot_chunks / 2;
+      rotate = false;
+    }
+  } else {
+    rotate = c < rot_chunks;
+  }
+  const int b = static_cast<int>(token / a.seq);
+  const int l = static_cast<int>(token % a.seq);
+  const int pos = (a.start ? a.start[b] : a.start_pos) + l;
+
+  float cs[8], sn[8];
+  if (rotate) {
+    const int n_ang = kNeox ? 8 : 4;
+    const int i0 = kNeox ? 8 * c : 4 * c;
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      if (t < n_ang) {
+        const float freq = powf(a.freq_base, -2.0f * static_cast<float>(i0 + t) / static_cast<float>(a.rotary_dim));
+        const float ang = static_cast<float>(pos) * freq;
+        sincosf(ang, &sn[t], &cs[t]);
+      }
+    }
+  }
+
+  auto rot8 = [&](const uint8_t* src, const uint8_t* src2, uint8_t* dst, uint8_t* dst2) {
+    // src/dst: chunk c of one head row; src2/dst2: the neox partner chunk
+    float x[8];
+    unpack8<BF16>(*reinterpret_cast<const uint4*>(src), x);
+    if (!rotate) {
+      if (dst != src) *reinterpret_cast<uint4*>(dst) = pack8<BF16>(x);
+      return;
+    }
+    if (kNeox) {
+      float y[8];
+      unpack8<BF16>(*reinterpret_cast<const uint4*>(src2), y);
+      float ox[8], oy[8];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        ox[t] = x[t] * cs[t] - y[t] * sn[t];
+        oy[t] = x[t] * sn[t] + y[t] * cs[t];
+      }
+      *reinterpret_cast<uint4*>(dst) = pack8<BF16>(ox);
+      *reinterpret_cast<uint4*>(dst2) = pack8<BF16>(oy);
+    } else {
+      float o[8];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        o[2 * t] = x[2 * t] * cs[t] - x[2 * t + 1] * sn[t];
+        o[2 * t + 1] = x[2 * t] * sn[t] + x[2 * t + 1] * cs[t];
+      }
+      *reinterpret_cast<uint4*>(dst) = pack8<BF16>(o);
+    }
+  };
+
+  const size_t co = static_cast<size_t>(c) * 16, co2 = static_cast<size_t>(c2 < 0 ? 0 : c2) * 16;
+  // q: in place
+  if (a.q != nullptr && rotate) {
+    uint8_t* base = reinterpret_cast<uint8_t*>(a.q) + 2 * (static_cast<size_t>(b) * a.q_stride[0] + static_cast<size_t>(l) * a.q_stride[1]);
+    for (int h = 0; h < a.n_heads; ++h) {
+      uint8_t* row = base + 2 * static_cast<size_t>(h) * a.q_stride[2];
+      rot8(row + co, row + co2, row + co, row + co2);
+    }
+  }
+  // k: rotated, into the cache (or in place when there is no cache)
+  if (a.k != nullptr && (rotate || a.k_cache != nullptr)) {
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(a.k) + 2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(l) * a.kv_stride[1]);
+    for (int h = 0; h < a.n_kv_heads; ++h) {
+      const uint8_t* row = base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
+      uint8_t* drow = a.k_cache != nullptr
+                          ? reinterpret_cast<uint8_t*>(a.k_cache) + 2 * (static_cast<size_t>(b) * a.cache_stride[0] + static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(pos) * a.cache_stride[2])
+                          : const_cast<uint8_t*>(row);
+      rot8(row + co, row + co2, drow + co, drow + co2);
+    }
+  }
+  // v: copied into the cache
+  if (a.v != nullptr && a.v_cache != nullptr) {
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(a.v) + 2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(l) * a.kv_stride[1]);
+    for (int h = 0; h < a.n_kv_heads; ++h) {
+      const uint8_t* row = base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
+      uint8_t* drow = reinterpret_cast<uint8_t*>(a.v_cache) + 2 * (static_cast<size_t>(b) * a.cache_stride[0] + static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(pos) * a.cache_stride[2]);
+      *reinterpret_cast<uint4*>(drow + co) = *reinterpret_cast<const uint4*>(row + co);
+      if (c2 >= 0) *reinterpret_cast<uint4*>(drow + co2) = *reinterpret_cast<const uint4*>(row + co2);
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, bool neox, cudaStream_t stream) {
+  const int chunks = a.head_dim / 8;
+  const int work_chunks = neox ? chunks - a.rotary_dim / 16 : chunks;
+  const long long threads = static_cast<long long>(a.batch) * a.seq * work_chunks;
+  const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+  if (bf16) {
+    if (neox) rope_append_kernel<true, true><<<grid, 256, 0, stream>>>(a);
+    else rope_append_kernel<true, false><<<grid, 256, 0, stream>>>(a);
+  } else {
+    if (neox) rope_append_kernel<false, true><<<grid, 256, 0, stream>>>(a);
+    else rope_append_kernel<false, false><<<grid, 256, 0, stream>>>(a);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace minfer_attn

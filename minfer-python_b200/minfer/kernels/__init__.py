@@ -1,7 +1,8 @@
 """Dispatch facade with the reference's shape (src/minfer/kernels/__init__.py:2-18).
 
-Only the attention attributes exist: `flash_attn` keeps the reference's
-signature; `flash_attn_causal` and `flash_attn_decode` are additions.
+Only the attention path's attributes exist: `flash_attn`, `il_rope` and `neox_rope`
+keep the reference's signatures; `flash_attn_causal`, `flash_attn_decode` and
+`rope_kv_append` are additions.
 """
 
 
@@ -9,6 +10,10 @@ class KernelBackend:
     def __init__(self, backend: str):
         if backend == "torch_ext":
             from .torch_ext import flash_attn, flash_attn_causal, flash_attn_decode
+            from .torch_ext import il_rope, neox_rope, rope_kv_append
+            self.il_rope = il_rope
+            self.neox_rope = neox_rope
+            self.rope_kv_append = rope_kv_append
             self.flash_attn = flash_attn
             self.flash_attn_causal = flash_attn_causal
             self.flash_attn_decode = flash_attn_decode

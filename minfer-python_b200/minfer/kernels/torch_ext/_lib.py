@@ -20,6 +20,7 @@ EXPORTS = (
     "minfer_attn_prefill_workspace_bytes",
     "minfer_attn_decode",
     "minfer_attn_decode_static",
+    "minfer_attn_rope_append",
     "minfer_attn_decode_workspace_bytes",
     "minfer_attn_decode_default_chunk",
     "minfer_attn_strerror",
@@ -77,6 +78,31 @@ class DecodeParams(ctypes.Structure):
     ]
 
 
+class RopeParams(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p),
+        ("k", ctypes.c_void_p),
+        ("v", ctypes.c_void_p),
+        ("k_cache", ctypes.c_void_p),
+        ("v_cache", ctypes.c_void_p),
+        ("start", ctypes.c_void_p),
+        ("q_stride", ctypes.c_int64 * 3),
+        ("kv_stride", ctypes.c_int64 * 3),
+        ("cache_stride", ctypes.c_int64 * 3),
+        ("batch", ctypes.c_int32),
+        ("seq", ctypes.c_int32),
+        ("n_heads", ctypes.c_int32),
+        ("n_kv_heads", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("rotary_dim", ctypes.c_int32),
+        ("start_pos", ctypes.c_int32),
+        ("max_len", ctypes.c_int32),
+        ("dtype", ctypes.c_int32),
+        ("style", ctypes.c_int32),
+        ("freq_base", ctypes.c_float),
+    ]
+
+
 def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -92,6 +118,8 @@ def _load() -> ctypes.CDLL:
     lib.minfer_attn_decode.restype = ctypes.c_int
     lib.minfer_attn_decode_static.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
     lib.minfer_attn_decode_static.restype = ctypes.c_int
+    lib.minfer_attn_rope_append.argtypes = [ctypes.POINTER(RopeParams), ctypes.c_void_p]
+    lib.minfer_attn_rope_append.restype = ctypes.c_int
     lib.minfer_attn_decode_workspace_bytes.argtypes = [ctypes.c_int32] * 5
     lib.minfer_attn_decode_workspace_bytes.restype = ctypes.c_size_t
     lib.minfer_attn_decode_default_chunk.argtypes = [ctypes.c_int32] * 3

@@ -27,6 +27,11 @@ _DEFS = {
                   "Tensor(a!) mask, Tensor(a!) out) -> ()",
     "flash_attn_causal": "(Tensor q, Tensor k, Tensor v, Tensor(a!) out) -> ()",
     "flash_attn_decode": "(Tensor q, Tensor k_cache, Tensor v_cache, Tensor lens, Tensor(a!) out) -> ()",
+    # the reference's schemas (csrc/reg.cpp:25-26)
+    "il_rope": "(int rotary_dim, int start_pos, float freq_base, Tensor(a!) x) -> ()",
+    "neox_rope": "(int rotary_dim, int start_pos, float freq_base, Tensor(a!) x) -> ()",
+    "rope_kv_append": "(int rotary_dim, float freq_base, int style, Tensor(a!) q, Tensor k, Tensor v, "
+                      "Tensor(a!) k_cache, Tensor(a!) v_cache, Tensor start) -> ()",
 }
 _library = torch.library.Library("minfer", "FRAGMENT")
 for _name, _schema in _DEFS.items():
@@ -159,6 +164,65 @@ def _flash_attn_decode_cuda(q, k_cache, v_cache, lens, out) -> None:
         _lib.check(_lib.lib.minfer_attn_decode(ctypes.byref(p), ctypes.c_void_p(stream)), "minfer_attn_decode")
 
 
+def _rope_call(p: "_lib.RopeParams", device) -> None:
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib.lib.minfer_attn_rope_append(ctypes.byref(p), ctypes.c_void_p(stream)), "minfer_attn_rope_append")
+
+
+def _rope_inplace_cuda(style: int, rotary_dim, start_pos, freq_base, x) -> None:
+    # the checks of the reference's launcher (csrc/cuda/il_rope/op.cuh:27-31), bfloat16 admitted
+    torch._check(x.is_cuda, lambda: "x must be on CUDA")
+    torch._check(x.is_contiguous(), lambda: "x must be contiguous")
+    torch._check(x.dim() == 4, lambda: "x must be [B, L, n_heads, head_dim]")
+    torch._check(rotary_dim <= x.size(3), lambda: "rotary_dim exceeds head_dim")
+    p = _lib.RopeParams()
+    p.q = x.data_ptr()
+    for i in range(3):
+        p.q_stride[i] = x.stride(i)
+    p.batch, p.seq, p.n_heads, p.head_dim = x.size(0), x.size(1), x.size(2), x.size(3)
+    p.rotary_dim, p.start_pos, p.freq_base = rotary_dim, start_pos, freq_base
+    p.dtype, p.style = _dtype_tag(x), style
+    _rope_call(p, x.device)
+
+
+def _il_rope_cuda(rotary_dim, start_pos, freq_base, x) -> None:
+    _rope_inplace_cuda(0, rotary_dim, start_pos, freq_base, x)
+
+
+def _neox_rope_cuda(rotary_dim, start_pos, freq_base, x) -> None:
+    _rope_inplace_cuda(1, rotary_dim, start_pos, freq_base, x)
+
+
+def _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start) -> None:
+    torch._check(q.is_cuda and k.is_cuda and v.is_cuda and k_cache.is_cuda and v_cache.is_cuda and start.is_cuda,
+                 lambda: "all tensors must be on CUDA")
+    torch._check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and k_cache.dim() == 4 and v_cache.dim() == 4,
+                 lambda: "q/k/v must be [B, L, H, D] and the caches [B, Hkv, Lmax, D]")
+    torch._check(q.dtype == k.dtype == v.dtype == k_cache.dtype == v_cache.dtype, lambda: "dtypes differ")
+    torch._check(k.shape == v.shape and k.stride() == v.stride(), lambda: "k and v must share shape and strides")
+    torch._check(k_cache.shape == v_cache.shape and k_cache.stride() == v_cache.stride(),
+                 lambda: "the caches must share shape and strides")
+    torch._check(q.size(0) == k.size(0) == k_cache.size(0) and q.size(1) == k.size(1), lambda: "batch / seq mismatch")
+    torch._check(k.size(2) == k_cache.size(1) and q.size(3) == k.size(3) == k_cache.size(3),
+                 lambda: "head count / head_dim mismatch")
+    torch._check(q.stride(-1) == 1 and k.stride(-1) == 1 and k_cache.stride(-1) == 1, lambda: "innermost stride must be 1")
+    torch._check(start.dtype == torch.int32 and start.dim() == 1 and start.numel() == q.size(0) and start.is_contiguous(),
+                 lambda: "start must be a contiguous int32 vector with one entry per sequence")
+    p = _lib.RopeParams()
+    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    p.k_cache, p.v_cache, p.start = k_cache.data_ptr(), v_cache.data_ptr(), start.data_ptr()
+    for i in range(3):
+        p.q_stride[i], p.kv_stride[i], p.cache_stride[i] = q.stride(i), k.stride(i), k_cache.stride(i)
+    p.batch, p.seq, p.n_heads, p.n_kv_heads, p.head_dim = q.size(0), q.size(1), q.size(2), k.size(2), q.size(3)
+    p.rotary_dim, p.start_pos, p.max_len, p.freq_base = rotary_dim, 0, k_cache.size(2), freq_base
+    p.dtype, p.style = _dtype_tag(q), style
+    _rope_call(p, q.device)
+
+
+_library.impl("il_rope", _il_rope_cuda, "CUDA")
+_library.impl("neox_rope", _neox_rope_cuda, "CUDA")
+_library.impl("rope_kv_append", _rope_kv_append_cuda, "CUDA")
 _library.impl("flash_attn", _flash_attn_cuda, "CUDA")
 _library.impl("flash_attn_causal", _flash_attn_causal_cuda, "CUDA")
 _library.impl("flash_attn_decode", _flash_attn_decode_cuda, "CUDA")
@@ -194,6 +258,54 @@ def flash_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     [B, n_kv_heads, max_len, D], lens int32 [B]; sequence b attends keys [0, lens[b]).
     """
     return torch.ops.minfer.flash_attn_decode.default(q, k_cache, v_cache, lens, out)
+
+
+def il_rope(rotary_dim: int, start_pos: int, freq_base: float, x: torch.Tensor):
+    """
+    Applies il_rope in-place (per-head): interleaved pairs of x [B, L, n_heads, head_dim]
+    """
+    return torch.ops.minfer.il_rope.default(rotary_dim, start_pos, freq_base, x)
+
+
+def neox_rope(rotary_dim: int, start_pos: int, freq_base: float, x: torch.Tensor):
+    """
+    Applies neox_rope in-place (per-head): halves of x [B, L, n_heads, head_dim]
+    """
+    return torch.ops.minfer.neox_rope.default(rotary_dim, start_pos, freq_base, x)
+
+
+def rope_kv_append(rotary_dim: int, freq_base: float, style: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                   k_cache: torch.Tensor, v_cache: torch.Tensor, start: torch.Tensor):
+    """
+    one pass before attention: rotate q [B, L, Hq, D] in place, write rotated k and plain v
+    [B, L, Hkv, D] into the caches [B, Hkv, Lmax, D] at rows start[b] + l (start: int32 [B]).
+    style 0 = interleaved (il_rope), 1 = neox.
+    """
+    return torch.ops.minfer.rope_kv_append.default(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start)
+
+
+@torch.library.register_fake("minfer::il_rope")
+def _(rotary_dim, start_pos, freq_base, x):
+    torch._check(x.dtype in (torch.float16, torch.bfloat16))
+    torch._check(x.dim() == 4)
+    torch._check(x.device.type == "cuda")
+    torch._check(rotary_dim <= x.size(3))
+
+
+@torch.library.register_fake("minfer::neox_rope")
+def _(rotary_dim, start_pos, freq_base, x):
+    torch._check(x.dtype in (torch.float16, torch.bfloat16))
+    torch._check(x.dim() == 4)
+    torch._check(x.device.type == "cuda")
+    torch._check(rotary_dim <= x.size(3))
+
+
+@torch.library.register_fake("minfer::rope_kv_append")
+def _(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start):
+    torch._check(q.dtype in (torch.float16, torch.bfloat16))
+    torch._check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and k_cache.dim() == 4 and v_cache.dim() == 4)
+    torch._check(start.dtype == torch.int32)
+    torch._check(q.device.type == "cuda")
 
 
 @torch.library.register_fake("minfer::flash_attn")

@@ -136,6 +136,36 @@ def decode_oracle(q, k_cache, v_cache, lens) -> torch.Tensor:
     return F.scaled_dot_product_attention(qf, kf, vf, attn_mask=m, enable_gqa=(kf.shape[1] != H))
 
 
+def il_rope_reference(x: torch.Tensor, rotary_dim: int, start_pos: int, base_freq: float) -> torch.Tensor:
+    """Interleaved RoPE restated from the reference (src/minfer/kernels/refs.py:12-28): fp32 angles
+    (pos + start_pos) * base^(-2i/rot), complex rotation of pairs (2i, 2i+1); x is [B, L, H, D]."""
+    rot = rotary_dim
+    f = torch.arange(rot // 2, dtype=torch.float32)
+    f = base_freq ** (-2.0 * f / rot)
+    ang = (torch.arange(x.shape[1], dtype=torch.float32) + start_pos)[:, None] * f[None, :]
+    c, s_ = torch.cos(ang)[None, :, None, :], torch.sin(ang)[None, :, None, :]
+    xf = x.float().clone()
+    a, b = xf[..., 0:rot:2].clone(), xf[..., 1:rot:2].clone()
+    xf[..., 0:rot:2] = a * c - b * s_
+    xf[..., 1:rot:2] = a * s_ + b * c
+    return xf.to(x.dtype)
+
+
+def neox_rope_reference(x: torch.Tensor, rotary_dim: int, start_pos: int, base_freq: float) -> torch.Tensor:
+    """Two-halves RoPE restated from the reference (src/minfer/kernels/refs.py:30-47): pairs
+    (i, i + rot/2)."""
+    rot = rotary_dim
+    f = torch.arange(rot // 2, dtype=torch.float32)
+    f = base_freq ** (-2.0 * f / rot)
+    ang = (torch.arange(x.shape[1], dtype=torch.float32) + start_pos)[:, None] * f[None, :]
+    c, s_ = torch.cos(ang)[None, :, None, :], torch.sin(ang)[None, :, None, :]
+    xf = x.float().clone()
+    a, b = xf[..., : rot // 2].clone(), xf[..., rot // 2:rot].clone()
+    xf[..., : rot // 2] = a * c - b * s_
+    xf[..., rot // 2:rot] = a * s_ + b * c
+    return xf.to(x.dtype)
+
+
 def within_tolerance(actual: torch.Tensor, expected: torch.Tensor, atol: float = 2e-3, rtol: float = 2e-3):
     """allclose with the path's stated tolerance; returns (ok, max_abs_err, n_bad)."""
     a = actual.detach().float().cpu()

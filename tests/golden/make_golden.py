@@ -114,6 +114,22 @@ def main():
                               vc.float().repeat_interleave(n_rep, dim=1), mask)
         np.savez(os.path.join(HERE, name + ".npz"), q=bits16(q), k=bits16(kc), v=bits16(vc),
                  lens=lens_t.numpy(), out=out.numpy(), bf16=np.array(dtype == torch.bfloat16))
+    # RoPE: the reference's il_rope / neox_rope oracles (refs.py:12-47) on fp16 inputs [B, L, H, D].
+    # Those functions broadcast their [L, rot/2] angle table against the HEAD axis of x, so they
+    # only run for L == 1; the vectors are therefore assembled one token at a time, token l being
+    # rotated by a call with start_pos + l — the per-token position the reference's CUDA kernels use
+    # (csrc/cuda/il_rope/kernel.cuh:17-23).
+    def per_token(fn, x, rot, start, base):
+        return torch.cat([fn(x[:, l:l + 1].clone(), rot, start + l, base) for l in range(x.shape[1])], dim=1)
+    for name, seed, B, L, H, D, rot, base in [("rope_d128_rot64", 31, 2, 40, 3, 128, 64, 1e6),
+                                              ("rope_d64_rot64", 32, 1, 24, 2, 64, 64, 500000.0)]:
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(B, L, H, D, generator=g).half()
+        out = {}
+        for start in (0, 2048):
+            out[f"il_{start}"] = bits16(per_token(refs.il_rope, x, rot, start, base))
+            out[f"neox_{start}"] = bits16(per_token(refs.neox_rope, x, rot, start, base))
+        np.savez(os.path.join(HERE, name + ".npz"), x=bits16(x), rot=np.array(rot), base=np.array(base), **out)
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 
