@@ -106,13 +106,18 @@ typedef struct MinferAttnPrefillParams {
 int minfer_attn_prefill(const MinferAttnPrefillParams* params, void* stream);
 
 /*
- * Scratch for calls with a dense mask.  When `workspace` holds at least this
- * many bytes, one pass over the mask classifies its 128 x 128 tiles (nothing
- * visible / everything visible / mixed); the attention kernel then skips tiles
- * nobody can see and reads mask bytes only for mixed ones, so a dense causal or
- * sliding-window mask costs about what the structure it encodes costs.  Without
- * a workspace (NULL) every tile is visited and masked byte by byte: same
- * result, more time.  Unused by causal calls.  Returns 0 for invalid sizes.
+ * Optional scratch of a prefill call (device memory, 16-byte aligned).
+ * Dense mask: when `workspace` holds at least this many bytes, one pass over the
+ * mask classifies its 128 x 128 tiles (nothing visible / everything visible /
+ * mixed); the attention kernel then skips tiles nobody can see and reads mask
+ * bytes only for mixed ones, so a dense causal or sliding-window mask costs about
+ * what the structure it encodes costs.  Without it every tile is visited and
+ * masked byte by byte.  Causal / unmasked calls: the first 4 bytes serve as a
+ * counter from which the persistent thread blocks claim work items (zeroed by the
+ * call on `stream`); without it the items are dealt out in a fixed order.  The
+ * result is the same with or without a workspace, only the time differs.  Calls
+ * that may overlap on the GPU need separate workspaces.  Returns 0 for invalid
+ * sizes, else at least 16.
  */
 size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t seq_k);
 

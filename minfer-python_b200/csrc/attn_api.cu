@@ -156,6 +156,10 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
   a.out = p->out;
   a.mask = p->causal ? nullptr : p->mask;
   a.cls = nullptr;
+  a.counter = nullptr;
+  // causal / unmasked calls: the first word of a (16-byte aligned) workspace is the work-item counter
+  if (a.mask == nullptr && p->workspace != nullptr && p->workspace_bytes >= 16 && aligned16(p->workspace))
+    a.counter = static_cast<int*>(p->workspace);
   if (a.mask != nullptr) {
     const size_t need = minfer_attn_prefill_workspace_bytes(p->batch, p->seq_q, p->seq_k);
     if (p->workspace != nullptr && p->workspace_bytes >= need && !(p->flags & MINFER_ATTN_FLAG_SIMPLE_KERNEL)) {
@@ -169,6 +173,7 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
   for (int i = 0; i < 3; ++i) a.out_stride[i] = p->out_stride[i];
   a.batch = p->batch;
   a.n_heads = p->n_heads;
+  a.n_kv_heads = p->n_kv_heads;
   a.seq_q = p->seq_q;
   a.seq_k = p->seq_k;
   a.group = p->n_heads / p->n_kv_heads;
@@ -189,7 +194,8 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
 
 size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t seq_k) {
   if (batch <= 0 || seq_q <= 0 || seq_k <= 0) return 0;
-  return static_cast<size_t>(batch) * ((seq_q + 127) / 128) * ((seq_k + 127) / 128);
+  const size_t cls = static_cast<size_t>(batch) * ((seq_q + 127) / 128) * ((seq_k + 127) / 128);
+  return cls < 16 ? 16 : cls;  // at least the work-item counter of causal calls
 }
 
 int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {

@@ -17,13 +17,15 @@ struct PrefillArgs {
   const uint8_t* mask;
   const uint8_t* cls;     // per (batch, query tile, key tile) mask class, or null: see mask_classify.cu
   int32_t* status;
+  int* counter;           // persistent kernel: work-item counter in the caller's workspace, or null (static order)
   int64_t out_stride[3];  // elements: batch, head, row
-  int32_t batch, n_heads, seq_q, seq_k;
+  int32_t batch, n_heads, n_kv_heads, seq_q, seq_k;
   int32_t group;          // query heads per kv head
   int32_t causal;
   int32_t mask_vec;       // mask rows may be read with 16-byte loads
   int32_t pair_heads;     // two-tile kernel: slots are two heads of one kv head (else two row tiles)
   int32_t items_x, items_y;  // persistent kernel: work-item grid (query tile [pairs], head [pairs]); set by its launcher
+  int32_t order_by_kv_set;   // persistent kernel, dynamic claiming: item order (see its launcher)
   float scale_log2;       // softmax scale * log2(e)
   // position (1..3) of the batch / head / row coordinate inside each tensor
   // map; coordinate 0 is always head_dim

@@ -14,9 +14,12 @@
 // .../flash_attn/kernels/kernel.cuh:16-27).
 //
 // Work items are (query tile or tile pair, head pair or head, batch) ordered by
-// decreasing number of key tiles; CTA c takes items c, 2G-1-c, 2G+c, ... (a snake
-// over rounds of G = gridDim.x items) so every CTA gets the same mix of long and
-// short items without a global counter.
+// decreasing number of key tiles.  With a counter in the caller's workspace the
+// CTAs claim items dynamically (longest first, whoever is free takes the next):
+// the TMA warp does the atomicAdd and publishes the item through a small
+// shared-memory ring to the other roles.  Without a workspace CTA c takes items
+// c, 2G-1-c, 2G+c, ... (a snake over rounds of G = gridDim.x items), which gives
+// every CTA the same mix of long and short items without any global state.
 //
 // Hand-offs between items, per slot s (all counted over the CTA's lifetime, so
 // mbarrier parities keep alternating):
@@ -50,7 +53,9 @@ constexpr int kSFull = 4;
 constexpr int kPFull = 6;
 constexpr int kODone = 8;
 constexpr int kOFree = 10;
-constexpr int kKvFull = 12;  // [kStages], then kKvEmpty [kStages]
+constexpr int kSched = 12;   // [kSchedRing] item published by the TMA warp
+constexpr int kSchedRing = 4; // the TMA warp is never more than two items ahead of the slowest role
+constexpr int kKvFull = 16;  // [kStages], then kKvEmpty [kStages]
 
 __device__ __forceinline__ void report_p(int32_t* status, int site) {
   if (status != nullptr && atomicCAS(status, 0, kStatusWaitTimeout) == 0) {
@@ -66,14 +71,26 @@ struct Item {
   int head[2], q0[2], n[2];
 };
 
-__device__ __forceinline__ Item decode_item(const PrefillArgs& a, int id) {
-  // id runs over [0, n_x * n_y * batch), long (late) query tiles first
+__device__ __forceinline__ Item decode_item(const PrefillArgs& a, int id, bool by_kv_set) {
   Item it;
-  const int per_x = a.items_y * a.batch;
-  const int xr = a.items_x - 1 - id / per_x;
-  const int rem = id % per_x;
-  const int y = rem % a.items_y;
-  it.b = rem / a.items_y;
+  int xr, y;
+  if (by_kv_set) {
+    // dynamic claiming: all items of one (batch, kv head) are adjacent, long query tiles first, so the
+    // CTAs running at any moment share a few K/V sets in L2; the list ends with short items
+    const int per_kv = a.items_y / a.n_kv_heads;  // head pairs (or heads) per kv head
+    const int per_set = a.items_x * per_kv;
+    const int set = id / per_set, w = id % per_set;
+    xr = a.items_x - 1 - w / per_kv;
+    y = (set % a.n_kv_heads) * per_kv + w % per_kv;
+    it.b = set / a.n_kv_heads;
+  } else {
+    // static dealing: globally longest first, so that a snake over rounds balances the CTAs
+    const int per_x = a.items_y * a.batch;
+    xr = a.items_x - 1 - id / per_x;
+    const int rem = id % per_x;
+    y = rem % a.items_y;
+    it.b = rem / a.items_y;
+  }
   if (a.pair_heads) {
     it.head[0] = 2 * y;
     it.head[1] = 2 * y + 1;
@@ -128,10 +145,19 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_kv + kStages * kTileBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* sched_id = reinterpret_cast<volatile int*>(tmem_slot + 4);  // [kSchedRing]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int n_items = a.items_x * a.items_y * a.batch;
+  const bool dynamic = a.counter != nullptr;
+  // k-th item of this CTA as seen by a consumer role (MMA, softmax): from the ring
+  // when items are claimed dynamically, else by the static rule; -1 = no more
+  auto next_item = [&](int k, bool& ok) -> int {
+    if (!dynamic) return item_id(k, n_items);
+    if (!(ok = mbar_wait(&bars[kSched + k % kSchedRing], (k / kSchedRing) & 1, abort_flag))) return -1;
+    return sched_id[k % kSchedRing];
+  };
 
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -142,6 +168,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_init(&bars[kODone + i], 1);
       mbar_init(&bars[kOFree + i], 128);
     }
+    for (int i = 0; i < kSchedRing; ++i) mbar_init(&bars[kSched + i], 1);
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&bars[kKvFull + i], 1);
       mbar_init(&bars[kKvEmpty + i], 1);
@@ -186,10 +213,27 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       bool ok = true;
       uint32_t q_loads[2] = {0u, 0u};  // Q tiles loaded so far per slot
       uint32_t r = 0;                  // K/V ring position over the CTA's lifetime
+      const int leader_lane = __ffs(__ballot_sync(0xFFFFFFFFu, leader)) - 1;
       for (int k = 0; ok; ++k) {
-        const int id = item_id(k, n_items);
+        int id;
+        if (dynamic) {
+          // first item: the CTA's own index; later ones from the global counter
+          id = static_cast<int>(blockIdx.x);
+          if (k > 0) {
+            if (leader) id = static_cast<int>(gridDim.x) + atomicAdd(a.counter, 1);
+            id = __shfl_sync(0xFFFFFFFFu, id, leader_lane);
+          }
+          if (id >= n_items) id = -1;
+          if (leader) {
+            sched_id[k % kSchedRing] = id;
+            __threadfence_block();
+            mbar_arrive(&bars[kSched + k % kSchedRing]);
+          }
+        } else {
+          id = item_id(k, n_items);
+        }
         if (id < 0) break;
-        const Item it = decode_item(a, id);
+        const Item it = decode_item(a, id, dynamic && a.order_by_kv_set);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           if (it.n[s] == 0 || !ok) continue;
@@ -270,9 +314,10 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       uint32_t items[2] = {0u, 0u};  // items started per slot (parity of q_full / o_free)
       uint32_t r = 0;                // K/V ring position, in step with the TMA warp
       for (int k = 0; ok; ++k) {
-        const int id = item_id(k, n_items);
+        const int id = next_item(k, ok);
+        if (!ok) { report_p(a.status, 37); break; }
         if (id < 0) break;
-        const Item it = decode_item(a, id);
+        const Item it = decode_item(a, id, dynamic && a.order_by_kv_set);
         const int n_max = max(it.n[0], it.n[1]);
         if (n_max == 0) continue;
 #pragma unroll
@@ -349,9 +394,10 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     uint32_t jt = 0;  // key tiles this slot has processed over the CTA's lifetime
 
     for (int k = 0; ok; ++k) {
-      const int id = item_id(k, n_items);
+      const int id = next_item(k, ok);
+      if (!ok) { report_p(a.status, 43); break; }
       if (id < 0) break;
-      const Item it = decode_item(a, id);
+      const Item it = decode_item(a, id, dynamic && a.order_by_kv_set);
       const int nt = s ? it.n[1] : it.n[0];
       if (nt == 0) continue;
       const int q0s = s ? it.q0[1] : it.q0[0];
@@ -505,6 +551,15 @@ cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, con
   const long long n_items = static_cast<long long>(a.items_x) * a.items_y * a.batch;
   if (n_items > 0x7FFFFFFF) return cudaErrorInvalidValue;
   const int grid = static_cast<int>(n_items < sm_count[dev] ? n_items : sm_count[dev]);
+  // Order of the dynamically claimed items: globally longest-first while all K/V of the call fit
+  // comfortably in the 126 MB L2; grouped by (batch, kv head) beyond that, so that the CTAs running
+  // at one time share a few K/V sets instead of sweeping all of them.
+  const double kv_bytes = 4.0 * a.batch * a.n_kv_heads * static_cast<double>(a.seq_k) * D;
+  a.order_by_kv_set = kv_bytes > 96.0 * 1024 * 1024 ? 1 : 0;
+  if (a.counter != nullptr) {
+    e = cudaMemsetAsync(a.counter, 0, sizeof(int), stream);
+    if (e != cudaSuccess) return e;
+  }
   prefill_persist_kernel<D, BF16><<<grid, kThreads, smem, stream>>>(tq, tk, tv, a);
   return cudaGetLastError();
 }

@@ -99,10 +99,10 @@ def _prefill(q, k, v, mask, out, causal: bool) -> None:
     p.causal = 1 if causal else 0
     p.softmax_scale = 0.0
     p.flags = (1 if _SIMPLE else 0) | _FLAGS
-    if mask is not None:
-        need = _lib.lib.minfer_attn_prefill_workspace_bytes(p.batch, p.seq_q, p.seq_k)
-        ws = _workspace_for(q.device, need, _mask_workspace)
-        p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    # mask tile classes (dense mask) or the persistent kernel's work-item counter (causal)
+    need = _lib.lib.minfer_attn_prefill_workspace_bytes(p.batch, p.seq_q, p.seq_k) if mask is not None else 16
+    ws = _workspace_for(q.device, need, _mask_workspace, torch.cuda.current_stream(q.device).cuda_stream)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
         _lib.check(_lib.lib.minfer_attn_prefill(ctypes.byref(p), ctypes.c_void_p(stream)), "minfer_attn_prefill")
@@ -126,9 +126,10 @@ def _flash_attn_causal_cuda(q, k, v, out) -> None:
     _prefill(q, k, v, None, out, causal=True)
 
 
-def _workspace_for(device: torch.device, nbytes: int, cache: dict) -> torch.Tensor:
-    """Per-device scratch owned by this layer (the library itself never allocates); grown on demand."""
-    idx = device.index if device.index is not None else torch.cuda.current_device()
+def _workspace_for(device: torch.device, nbytes: int, cache: dict, stream: int = 0) -> torch.Tensor:
+    """Scratch owned by this layer (the library itself never allocates), one buffer per device and
+    stream so that calls on different streams never share one; grown on demand."""
+    idx = (device.index if device.index is not None else torch.cuda.current_device(), stream)
     t = cache.get(idx)
     if t is None or t.numel() < nbytes:
         t = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)

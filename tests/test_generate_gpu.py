@@ -1,5 +1,6 @@
 """GPU: the generate app's decoder (prefill -> cache -> decode steps on the package's ops) against an
 fp32 CPU twin that recomputes full causal attention with the oracle at every step (teacher-forced)."""
+import importlib.util
 import os
 import sys
 
@@ -11,6 +12,15 @@ from conftest import PKG_ROOT
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
+
+
+def load_generate_app():
+    """Import apps/generate.py by path (putting apps/ on sys.path would shadow the stdlib `profile`)."""
+    spec = importlib.util.spec_from_file_location("minfer_generate_app", os.path.join(PKG_ROOT, "apps", "generate.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod  # dataclasses look their module up there
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def twin_logits(model, tokens):
@@ -37,8 +47,7 @@ def twin_logits(model, tokens):
 
 @pytest.mark.parametrize("rope_style,head_dim", [(0, 64), (1, 128)])
 def test_prefill_then_decode_matches_twin(rope_style, head_dim):
-    sys.path.insert(0, os.path.join(PKG_ROOT, "apps"))
-    import generate as G
+    G = load_generate_app()
     shape = G.Shape(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=head_dim, ffn=512, vocab=500,
                     rope_theta=500000.0, rope_style=rope_style)
     B, L, steps = 2, 150, 4
@@ -59,8 +68,7 @@ def test_prefill_then_decode_matches_twin(rope_style, head_dim):
 
 
 def test_generate_runs_and_reports():
-    sys.path.insert(0, os.path.join(PKG_ROOT, "apps"))
-    import generate as G
+    G = load_generate_app()
     shape = G.Shape(layers=2, hidden=256, heads=8, kv_heads=2, head_dim=64, ffn=512, vocab=300)
     model = G.Decoder(shape, 3, 64 + 6)
     prompts = torch.randint(0, 300, (3, 64), generator=torch.Generator().manual_seed(1)).cuda()
