@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define MINFER_ATTN_ABI_VERSION 2
+#define MINFER_ATTN_ABI_VERSION 3
 
 /* element types of q/k/v/out */
 #define MINFER_ATTN_F16  0
@@ -44,6 +44,10 @@ extern "C" {
  * persistent form (one block per SM walking a list of items).  Dense-mask calls
  * always run this way.  Kept for cross-checking. */
 #define MINFER_ATTN_FLAG_ONE_ITEM_PER_CTA 2
+
+/* KV-cache formats (kv_format / cache_format fields) */
+#define MINFER_ATTN_KV_16BIT 0  /* the same 16-bit type as q                                    */
+#define MINFER_ATTN_KV_Q8_0  1  /* GGML Q8_0 blocks: 32 int8 + one fp16 scale = 34 bytes        */
 
 /* error codes */
 #define MINFER_ATTN_OK            0
@@ -138,6 +142,14 @@ size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t
  * a device buffer of at least minfer_attn_decode_workspace_bytes() bytes that
  * the caller owns.  chunk == 0 lets the library choose; otherwise it must be a
  * positive multiple of 64.
+ *
+ * kv_format == MINFER_ATTN_KV_Q8_0: the caches hold GGML Q8_0 blocks (the
+ * reference's block_q8_0, csrc/common/types.hpp:141-146): a cache row is
+ * head_dim/32 blocks of 34 bytes, rows of one (batch, head) are contiguous,
+ * kv_stride[0] and kv_stride[1] are then in BYTES (multiples of 16) and
+ * kv_stride[2] is ignored; max_len must be even.  Every cached value is used as
+ * (16-bit type)(q * d), the reference's dequant_row_q8_0 (csrc/quants/impl.cpp:
+ * 1153-1166), so the result equals the 16-bit path run on the dequantised cache.
  */
 typedef struct MinferAttnDecodeParams {
   const void*    q;
@@ -158,6 +170,7 @@ typedef struct MinferAttnDecodeParams {
   int32_t dtype;
   int32_t chunk;
   float   softmax_scale;
+  int32_t kv_format;      /* MINFER_ATTN_KV_16BIT (0) or MINFER_ATTN_KV_Q8_0 */
 } MinferAttnDecodeParams;
 
 int minfer_attn_decode(const MinferAttnDecodeParams* params, void* stream);
@@ -215,6 +228,12 @@ int minfer_attn_decode_static(const MinferAttnDecodeParams* params, void* stream
  * a multiple of 8 (16 for the neox style) and at most head_dim; head_dim is a
  * multiple of 8.  style: 0 = interleaved pairs, 1 = neox (two halves).
  * The caller guarantees start[b] + seq <= max_len.
+ *
+ * cache_format == MINFER_ATTN_KV_Q8_0: the caches hold Q8_0 blocks (layout as for
+ * minfer_attn_decode; cache_stride[0..1] in bytes, [2] ignored): the row the
+ * 16-bit cache would receive is quantised as the reference's quant_row_q8_0 does
+ * (csrc/quants/impl.cpp:1169-1193).  Needs head_dim % 32 == 0, and for the neox
+ * style rotary_dim % 64 == 0.
  */
 typedef struct MinferRopeParams {
   void*          q;
@@ -237,6 +256,7 @@ typedef struct MinferRopeParams {
   int32_t dtype;
   int32_t style;
   float   freq_base;
+  int32_t cache_format;   /* MINFER_ATTN_KV_16BIT (0) or MINFER_ATTN_KV_Q8_0 */
 } MinferRopeParams;
 
 int minfer_attn_rope_append(const MinferRopeParams* params, void* stream);

@@ -212,9 +212,16 @@ int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {
     return MINFER_ATTN_EINVAL;
   if ((p->k != nullptr && !aligned16(p->k)) || (p->v != nullptr && !aligned16(p->v))) return MINFER_ATTN_EINVAL;
   if ((p->k_cache == nullptr) != (p->v_cache == nullptr)) return MINFER_ATTN_EINVAL;
+  const bool cq8 = p->cache_format == MINFER_ATTN_KV_Q8_0;
+  if (p->cache_format != MINFER_ATTN_KV_16BIT && !cq8) return MINFER_ATTN_EINVAL;
+  if (cq8 && (p->k_cache == nullptr || p->head_dim % 32 != 0 || (p->style == 1 && p->rotary_dim % 64 != 0)))
+    return MINFER_ATTN_EINVAL;
   if (p->k_cache != nullptr) {
     if (p->k == nullptr || p->v == nullptr) return MINFER_ATTN_EINVAL;
-    if (!aligned16(p->k_cache) || !aligned16(p->v_cache) || !strides_ok(p->cache_stride, 3)) return MINFER_ATTN_EINVAL;
+    if (!aligned16(p->k_cache) || !aligned16(p->v_cache)) return MINFER_ATTN_EINVAL;
+    if (cq8 ? (p->cache_stride[0] < 0 || p->cache_stride[1] < 0 || p->cache_stride[0] % 2 != 0 || p->cache_stride[1] % 2 != 0)
+            : !strides_ok(p->cache_stride, 3))
+      return MINFER_ATTN_EINVAL;
     if (p->max_len <= 0) return MINFER_ATTN_EINVAL;
     if (p->start == nullptr && (p->start_pos < 0 || p->start_pos + p->seq > p->max_len)) return MINFER_ATTN_EINVAL;
   }
@@ -241,6 +248,7 @@ int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {
   a.rotary_dim = p->rotary_dim;
   a.start_pos = p->start_pos;
   a.freq_base = p->freq_base;
+  a.cache_q8 = cq8 ? 1 : 0;
   return cuda_result(launch_rope_append(a, p->dtype == MINFER_ATTN_BF16, p->style == 1, static_cast<cudaStream_t>(stream)));
 }
 
@@ -270,8 +278,16 @@ int minfer_attn_decode(const MinferAttnDecodeParams* p, void* stream) {
   if (group > 16) return MINFER_ATTN_EUNSUPPORTED;
   if (!aligned16(p->q) || !aligned16(p->k_cache) || !aligned16(p->v_cache) || !aligned16(p->out))
     return MINFER_ATTN_EINVAL;
-  if (!strides_ok(p->q_stride, 2) || !strides_ok(p->kv_stride, 3) || !strides_ok(p->out_stride, 2))
+  const bool q8 = p->kv_format == MINFER_ATTN_KV_Q8_0;
+  if (p->kv_format != MINFER_ATTN_KV_16BIT && !q8) return MINFER_ATTN_EINVAL;
+  if (!strides_ok(p->q_stride, 2) || !strides_ok(p->out_stride, 2)) return MINFER_ATTN_EINVAL;
+  if (q8) {
+    if (p->kv_stride[0] < 0 || p->kv_stride[1] < 0 || p->kv_stride[0] % 16 != 0 || p->kv_stride[1] % 16 != 0)
+      return MINFER_ATTN_EINVAL;
+    if (p->max_len % 2 != 0) return MINFER_ATTN_EINVAL;
+  } else if (!strides_ok(p->kv_stride, 3)) {
     return MINFER_ATTN_EINVAL;
+  }
   if (!(p->softmax_scale >= 0.f)) return MINFER_ATTN_EINVAL;
   if (p->batch > 65535 || p->n_kv_heads > 65535) return MINFER_ATTN_EUNSUPPORTED;
   int32_t chunk = p->chunk;
@@ -305,7 +321,7 @@ int minfer_attn_decode(const MinferAttnDecodeParams* p, void* stream) {
   const float scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->head_dim));
   a.scale_log2 = scale * 1.4426950408889634f;
 
-  cudaError_t e = launch_decode(a, p->head_dim, p->dtype == MINFER_ATTN_BF16, static_cast<cudaStream_t>(stream));
+  cudaError_t e = launch_decode(a, p->head_dim, p->dtype == MINFER_ATTN_BF16, q8, static_cast<cudaStream_t>(stream));
   return cuda_result(e);
 }
 

@@ -58,6 +58,7 @@ struct RopeArgs {
   int64_t kv_stride[3];     // batch, token, head
   int64_t cache_stride[3];  // batch, head, row
   int32_t batch, seq, n_heads, n_kv_heads, head_dim, rotary_dim, start_pos;
+  int32_t cache_q8;         // caches hold GGML Q8_0 blocks; cache_stride then in bytes (batch, head), rows contiguous
   float freq_base;
 };
 cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, bool neox, cudaStream_t stream);
@@ -72,7 +73,7 @@ struct DecodeArgs {
   float* part_o;   // [batch, n_heads, n_split, head_dim] fp32, unnormalised
   float* part_ml;  // [batch, n_heads, n_split, 2] running max (log2 domain) and sum
   int64_t q_stride[2];
-  int64_t kv_stride[3];
+  int64_t kv_stride[3];   // elements; for a Q8_0 cache: bytes (batch, head), rows contiguous
   int64_t out_stride[2];
   int32_t batch, n_heads, n_kv_heads, max_len;
   int32_t group;
@@ -81,6 +82,6 @@ struct DecodeArgs {
   float scale_log2;
 };
 
-cudaError_t launch_decode(const DecodeArgs& a, int head_dim, bool bf16, cudaStream_t stream);
+cudaError_t launch_decode(const DecodeArgs& a, int head_dim, bool bf16, bool q8, cudaStream_t stream);
 
 }  // namespace minfer_attn

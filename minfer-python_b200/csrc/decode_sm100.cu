@@ -15,6 +15,14 @@
 // memory time.  The warps' states are merged through shared memory and written
 // as one fp32 partial (max, sum, unnormalised output) per (query head, split).
 //
+// Q8 = true: the caches hold GGML Q8_0 blocks (32 int8 + one fp16 scale, 34 bytes;
+// the reference's block_q8_0, src/minfer/kernels/torch_ext/csrc/common/types.hpp:141-146).
+// The raw bytes of a 16-key tile are contiguous in the cache and ride the same
+// cp.async ring; each warp then dequantises its tile into a 16-bit tile in
+// shared memory, value by value exactly as the reference's dequant_row_q8_0<half>
+// does ((half)(q * d), csrc/quants/impl.cpp:1153-1166), and the arithmetic above
+// runs unchanged.  Cache bytes per key drop from 4 D to 2.125 D.
+//
 // Kernel 2 (decode_combine_kernel): grid (n_heads, batch) merges the partials
 // of the ceil(len / chunk) splits of a sequence and writes the 16-bit output.
 #include "attn_internal.h"
@@ -38,13 +46,43 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
   else return row * 128 + (((chunk ^ row) & 7) << 4);
 }
 
-template <int D, bool BF16>
+// Eight values of one Q8_0 block (quarter `part` of its 32) -> eight 16-bit values at dst.
+// Each value is (16-bit type)(q * d) with d the block's fp16 scale: the product of an 8-bit integer
+// and an fp16 is exact in fp32, so this is one rounding, as in the reference's dequant_row_q8_0.
+// Dead rows (beyond the sequence) become zeros so that no stale byte can turn into Inf/NaN.
+template <bool BF16>
+__device__ __forceinline__ void dequant8(const uint8_t* block, int part, bool live, uint8_t* dst) {
+  uint4 out = make_uint4(0u, 0u, 0u, 0u);
+  if (live) {
+    const float d = __half2float(*reinterpret_cast<const __half*>(block));
+    const uint16_t* q16 = reinterpret_cast<const uint16_t*>(block + 2 + part * 8);  // 2-byte aligned
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t two = q16[i];
+      const float f0 = static_cast<float>(static_cast<int8_t>(two & 0xFFu)) * d;
+      const float f1 = static_cast<float>(static_cast<int8_t>(two >> 8)) * d;
+      w[i] = pack2<BF16>(f0, f1);
+    }
+    out = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  *reinterpret_cast<uint4*>(dst) = out;
+}
+
+template <int D, bool BF16, bool Q8>
 __global__ void __launch_bounds__(kWarps * 32, 2) decode_split_kernel(const DecodeArgs a) {
   constexpr int kRowBytes = D * 2;
-  constexpr int kTileBytes = kTileKeys * kRowBytes;        // one of K or V
+  constexpr int kTileBytes = kTileKeys * kRowBytes;        // one of K or V, 16-bit
   constexpr int kChunksPerRow = D / 8;                     // 16-byte chunks
   constexpr int kLoadsPerLane = kTileKeys * kChunksPerRow / 32;
-  constexpr int kWarpBytes = kStages * 2 * kTileBytes;
+  // Q8_0: raw rows of D/32 blocks of 34 bytes; a 16-row tile is one contiguous, 16-byte aligned span
+  constexpr int kQRowBytes = (D / 32) * 34;
+  constexpr int kQTileBytes = kTileKeys * kQRowBytes;      // 2176 (D=128) / 1088 (D=64): multiples of 16
+  constexpr int kQChunks = kQTileBytes / 16;
+  constexpr int kQLoadsPerLane = (kQChunks + 31) / 32;
+  // per warp: the ring of raw tiles, plus (Q8) one dequantised K and V tile
+  constexpr int kRingBytes = kStages * 2 * (Q8 ? kQTileBytes : kTileBytes);
+  constexpr int kWarpBytes = kRingBytes + (Q8 ? 2 * kTileBytes : 0);
 
   extern __shared__ __align__(128) uint8_t smem[];
 
@@ -73,6 +111,28 @@ __global__ void __launch_bounds__(kWarps * 32, 2) decode_split_kernel(const Deco
   auto issue_tile = [&](int i) {  // i-th tile of this warp -> stage i % kStages
     if (i < nt_w) {
       const int key0 = c0 + (warp + i * kWarps) * kTileKeys;
+      if constexpr (Q8) {
+        // strides of a Q8_0 cache are in bytes; rows are contiguous
+        const uint8_t* kq = reinterpret_cast<const uint8_t*>(a.k) + static_cast<size_t>(b) * a.kv_stride[0] +
+                            static_cast<size_t>(kvh) * a.kv_stride[1] + static_cast<size_t>(key0) * kQRowBytes;
+        const uint8_t* vq = reinterpret_cast<const uint8_t*>(a.v) + static_cast<size_t>(b) * a.kv_stride[0] +
+                            static_cast<size_t>(kvh) * a.kv_stride[1] + static_cast<size_t>(key0) * kQRowBytes;
+        uint8_t* dst_k = wsm + (i % kStages) * 2 * kQTileBytes;
+        uint8_t* dst_v = dst_k + kQTileBytes;
+        // bytes of live rows in this tile (rows beyond the sequence are neither read nor used)
+        const int live = min(kTileKeys, c1 - key0) * kQRowBytes;
+#pragma unroll
+        for (int t = 0; t < kQLoadsPerLane; ++t) {
+          const int ch = t * 32 + lane;
+          if (ch < kQChunks) {
+            const bool pred = ch * 16 < live;  // a chunk that starts inside a live row stays inside the cache
+            cp_async_16(dst_k + ch * 16, kq + (pred ? ch * 16 : 0), pred);
+            cp_async_16(dst_v + ch * 16, vq + (pred ? ch * 16 : 0), pred);
+          }
+        }
+        cp_async_commit();
+        return;
+      }
       uint8_t* dst_k = wsm + (i % kStages) * 2 * kTileBytes;
       uint8_t* dst_v = dst_k + kTileBytes;
 #pragma unroll
@@ -131,9 +191,32 @@ __global__ void __launch_bounds__(kWarps * 32, 2) decode_split_kernel(const Deco
     __syncwarp();
     issue_tile(i + kStages - 1);
 
-    const uint32_t sk = wsm_u32 + (i % kStages) * 2 * kTileBytes;
-    const uint32_t sv = sk + kTileBytes;
     const int key0 = c0 + (warp + i * kWarps) * kTileKeys;
+    uint32_t sk, sv;
+    if constexpr (Q8) {
+      // dequantise the raw tile into the warp's 16-bit K and V tiles (same swizzle as the 16-bit path)
+      const uint8_t* raw_k = wsm + (i % kStages) * 2 * kQTileBytes;
+      const uint8_t* raw_v = raw_k + kQTileBytes;
+      uint8_t* deq_k = wsm + kRingBytes;
+      uint8_t* deq_v = deq_k + kTileBytes;
+      const int live_rows = min(kTileKeys, c1 - key0);
+      __syncwarp();  // the previous tile's ldmatrix reads of deq_* are done
+#pragma unroll
+      for (int t = 0; t < kLoadsPerLane; ++t) {
+        const int idx = t * 32 + lane;
+        const int row = idx / kChunksPerRow;
+        const int chunk = idx % kChunksPerRow;
+        const int off = row * kQRowBytes + (chunk >> 2) * 34;  // the block holding elements 8*chunk .. 8*chunk+7
+        dequant8<BF16>(raw_k + off, chunk & 3, row < live_rows, deq_k + swz<D>(row, chunk));
+        dequant8<BF16>(raw_v + off, chunk & 3, row < live_rows, deq_v + swz<D>(row, chunk));
+      }
+      __syncwarp();
+      sk = wsm_u32 + kRingBytes;
+      sv = sk + kTileBytes;
+    } else {
+      sk = wsm_u32 + (i % kStages) * 2 * kTileBytes;
+      sv = sk + kTileBytes;
+    }
 
     // ---- S[16 heads x 16 keys] = Q K^T ----
     float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -282,20 +365,22 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
   else *reinterpret_cast<__half*>(op) = __float2half_rn(r);
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool Q8>
 cudaError_t launch_one(const DecodeArgs& a, cudaStream_t stream) {
-  constexpr int smem = kWarps * kStages * 2 * kTileKeys * D * 2;
+  constexpr int kRaw = Q8 ? kTileKeys * (D / 32) * 34 : kTileKeys * D * 2;
+  constexpr int smem = kWarps * (kStages * 2 * kRaw + (Q8 ? 2 * kTileKeys * D * 2 : 0));
+  static_assert(smem / kWarps >= 16 * D * 4 + 128, "the per-warp region also holds the fp32 merge buffer");
   static bool attr_done[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 64 && !attr_done[dev]) {
-    e = cudaFuncSetAttribute(decode_split_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(decode_split_kernel<D, BF16, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
   dim3 grid(a.n_split, a.n_kv_heads, a.batch);
-  decode_split_kernel<D, BF16><<<grid, kWarps * 32, smem, stream>>>(a);
+  decode_split_kernel<D, BF16, Q8><<<grid, kWarps * 32, smem, stream>>>(a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   decode_combine_kernel<D, BF16><<<dim3(a.n_heads, a.batch), D, 0, stream>>>(a);
@@ -304,9 +389,13 @@ cudaError_t launch_one(const DecodeArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
-cudaError_t launch_decode(const DecodeArgs& a, int head_dim, bool bf16, cudaStream_t stream) {
-  if (head_dim == 128) return bf16 ? launch_one<128, true>(a, stream) : launch_one<128, false>(a, stream);
-  return bf16 ? launch_one<64, true>(a, stream) : launch_one<64, false>(a, stream);
+cudaError_t launch_decode(const DecodeArgs& a, int head_dim, bool bf16, bool q8, cudaStream_t stream) {
+  if (q8) {
+    if (head_dim == 128) return bf16 ? launch_one<128, true, true>(a, stream) : launch_one<128, false, true>(a, stream);
+    return bf16 ? launch_one<64, true, true>(a, stream) : launch_one<64, false, true>(a, stream);
+  }
+  if (head_dim == 128) return bf16 ? launch_one<128, true, false>(a, stream) : launch_one<128, false, false>(a, stream);
+  return bf16 ? launch_one<64, true, false>(a, stream) : launch_one<64, false, false>(a, stream);
 }
 
 }  // namespace minfer_attn

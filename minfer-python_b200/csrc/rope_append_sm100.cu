@@ -16,6 +16,12 @@
 // of k/v costs nothing extra (the cache layout is the reference's,
 // src/minfer/core.py:105-127).
 //
+// With cache_q8 the caches hold GGML Q8_0 blocks instead (the reference's block_q8_0,
+// csrc/common/types.hpp:141-146): the row that the 16-bit cache would receive (rotated k,
+// plain v, rounded to the 16-bit type) is quantised as the reference's quant_row_q8_0 does
+// (csrc/quants/impl.cpp:1169-1193): d = max|x| / 127, q = roundf(x / d), 32 values per block.
+// The four threads that own one block's four chunks agree on the maximum with two shuffles.
+//
 // Thread mapping: a thread owns one token and one 16-byte chunk of head_dim
 // (neox: the chunk and its partner chunk) and loops over all heads, so the
 // sin/cos of its 4 (8) angles are computed once per token, not once per head.
@@ -62,6 +68,37 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// Quantise 8 values (this thread's quarter of a 32-value block) and store them into the Q8_0
+// block at `blk`; `part` = which quarter.  All four threads of the block call this together.
+__device__ __forceinline__ void store_q8_quarter(const float (&x)[8], uint8_t* blk, int part) {
+  float amax = 0.f;
+#pragma unroll
+  for (int t = 0; t < 8; ++t) amax = fmaxf(amax, fabsf(x[t]));
+  const unsigned mask = __activemask();
+  amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 2));
+  const float d = amax / 127.f;
+  const float id = d ? 1.0f / d : 0.0f;
+  if (part == 0) *reinterpret_cast<__half*>(blk) = __float2half_rn(d);
+  uint16_t* q16 = reinterpret_cast<uint16_t*>(blk + 2 + part * 8);  // 2-byte aligned
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int q0 = static_cast<int>(roundf(x[2 * t] * id));
+    const int q1 = static_cast<int>(roundf(x[2 * t + 1] * id));
+    q16[t] = static_cast<uint16_t>((q0 & 0xFF) | ((q1 & 0xFF) << 8));
+  }
+}
+
+// values as the 16-bit cache would hold them (rounded to the 16-bit type), back in fp32
+template <bool BF16>
+__device__ __forceinline__ void round16(float (&x)[8]) {
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    if constexpr (BF16) x[t] = __bfloat162float(__float2bfloat16_rn(x[t]));
+    else x[t] = __half2float(__float2half_rn(x[t]));
+  }
+}
+
 // kNeox = false: interleaved pairs; true: two halves.
 template <bool BF16, bool kNeox>
 __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
@@ -104,35 +141,42 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
     }
   }
 
-  auto rot8 = [&](const uint8_t* src, const uint8_t* src2, uint8_t* dst, uint8_t* dst2) {
-    // src/dst: chunk c of one head row; src2/dst2: the neox partner chunk
+  // rotate chunk c (and its neox partner c2) of one head row into fp32; returns false if nothing changed
+  auto rot8f = [&](const uint8_t* src, const uint8_t* src2, float (&ox)[8], float (&oy)[8]) {
     float x[8];
     unpack8<BF16>(*reinterpret_cast<const uint4*>(src), x);
     if (!rotate) {
-      if (dst != src) *reinterpret_cast<uint4*>(dst) = pack8<BF16>(x);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) ox[t] = x[t];
       return;
     }
     if (kNeox) {
       float y[8];
       unpack8<BF16>(*reinterpret_cast<const uint4*>(src2), y);
-      float ox[8], oy[8];
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
         ox[t] = x[t] * cs[t] - y[t] * sn[t];
         oy[t] = x[t] * sn[t] + y[t] * cs[t];
       }
-      *reinterpret_cast<uint4*>(dst) = pack8<BF16>(ox);
-      *reinterpret_cast<uint4*>(dst2) = pack8<BF16>(oy);
     } else {
-      float o[8];
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
-        o[2 * t] = x[2 * t] * cs[t] - x[2 * t + 1] * sn[t];
-        o[2 * t + 1] = x[2 * t] * sn[t] + x[2 * t + 1] * cs[t];
+        ox[2 * t] = x[2 * t] * cs[t] - x[2 * t + 1] * sn[t];
+        ox[2 * t + 1] = x[2 * t] * sn[t] + x[2 * t + 1] * cs[t];
       }
-      *reinterpret_cast<uint4*>(dst) = pack8<BF16>(o);
     }
   };
+  auto rot8 = [&](const uint8_t* src, const uint8_t* src2, uint8_t* dst, uint8_t* dst2) {
+    float ox[8], oy[8];
+    rot8f(src, src2, ox, oy);
+    if (!rotate) {
+      if (dst != src) *reinterpret_cast<uint4*>(dst) = pack8<BF16>(ox);
+      return;
+    }
+    *reinterpret_cast<uint4*>(dst) = pack8<BF16>(ox);
+    if (kNeox) *reinterpret_cast<uint4*>(dst2) = pack8<BF16>(oy);
+  };
+  const int q_row_bytes = (a.head_dim / 32) * 34;  // a Q8_0 cache row
 
   const size_t co = static_cast<size_t>(c) * 16, co2 = static_cast<size_t>(c2 < 0 ? 0 : c2) * 16;
   // q: in place
@@ -148,6 +192,19 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
     const uint8_t* base = reinterpret_cast<const uint8_t*>(a.k) + 2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(l) * a.kv_stride[1]);
     for (int h = 0; h < a.n_kv_heads; ++h) {
       const uint8_t* row = base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
+      if (a.cache_q8) {  // cache strides in bytes, rows contiguous
+        uint8_t* qrow = reinterpret_cast<uint8_t*>(a.k_cache) + static_cast<size_t>(b) * a.cache_stride[0] +
+                        static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(pos) * q_row_bytes;
+        float ox[8], oy[8];
+        rot8f(row + co, row + co2, ox, oy);
+        round16<BF16>(ox);
+        store_q8_quarter(ox, qrow + (c >> 2) * 34, c & 3);
+        if (c2 >= 0) {
+          round16<BF16>(oy);
+          store_q8_quarter(oy, qrow + (c2 >> 2) * 34, c2 & 3);
+        }
+        continue;
+      }
       uint8_t* drow = a.k_cache != nullptr
                           ? reinterpret_cast<uint8_t*>(a.k_cache) + 2 * (static_cast<size_t>(b) * a.cache_stride[0] + static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(pos) * a.cache_stride[2])
                           : const_cast<uint8_t*>(row);
@@ -159,6 +216,18 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
     const uint8_t* base = reinterpret_cast<const uint8_t*>(a.v) + 2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(l) * a.kv_stride[1]);
     for (int h = 0; h < a.n_kv_heads; ++h) {
       const uint8_t* row = base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
+      if (a.cache_q8) {
+        uint8_t* qrow = reinterpret_cast<uint8_t*>(a.v_cache) + static_cast<size_t>(b) * a.cache_stride[0] +
+                        static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(pos) * q_row_bytes;
+        float x[8];
+        unpack8<BF16>(*reinterpret_cast<const uint4*>(row + co), x);
+        store_q8_quarter(x, qrow + (c >> 2) * 34, c & 3);
+        if (c2 >= 0) {
+          unpack8<BF16>(*reinterpret_cast<const uint4*>(row + co2), x);
+          store_q8_quarter(x, qrow + (c2 >> 2) * 34, c2 & 3);
+        }
+        continue;
+      }
       uint8_t* drow = reinterpret_cast<uint8_t*>(a.v_cache) + 2 * (static_cast<size_t>(b) * a.cache_stride[0] + static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(pos) * a.cache_stride[2]);
       *reinterpret_cast<uint4*>(drow + co) = *reinterpret_cast<const uint4*>(row + co);
       if (c2 >= 0) *reinterpret_cast<uint4*>(drow + co2) = *reinterpret_cast<const uint4*>(row + co2);

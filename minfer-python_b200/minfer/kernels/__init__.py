@@ -11,6 +11,9 @@ class KernelBackend:
         if backend == "torch_ext":
             from .torch_ext import flash_attn, flash_attn_causal, flash_attn_decode
             from .torch_ext import il_rope, neox_rope, rope_kv_append
+            from .torch_ext import flash_attn_decode_q8, rope_kv_append_q8
+            self.flash_attn_decode_q8 = flash_attn_decode_q8
+            self.rope_kv_append_q8 = rope_kv_append_q8
             self.il_rope = il_rope
             self.neox_rope = neox_rope
             self.rope_kv_append = rope_kv_append

@@ -14,6 +14,8 @@ LIB_PATH = os.environ.get("MINFER_ATTN_LIBRARY") or os.path.join(_HERE, "libminf
 
 F16 = 0
 BF16 = 1
+KV_16BIT = 0
+KV_Q8_0 = 1
 
 EXPORTS = (
     "minfer_attn_prefill",
@@ -75,6 +77,7 @@ class DecodeParams(ctypes.Structure):
         ("dtype", ctypes.c_int32),
         ("chunk", ctypes.c_int32),
         ("softmax_scale", ctypes.c_float),
+        ("kv_format", ctypes.c_int32),
     ]
 
 
@@ -100,6 +103,7 @@ class RopeParams(ctypes.Structure):
         ("dtype", ctypes.c_int32),
         ("style", ctypes.c_int32),
         ("freq_base", ctypes.c_float),
+        ("cache_format", ctypes.c_int32),
     ]
 
 

@@ -32,6 +32,10 @@ _DEFS = {
     "neox_rope": "(int rotary_dim, int start_pos, float freq_base, Tensor(a!) x) -> ()",
     "rope_kv_append": "(int rotary_dim, float freq_base, int style, Tensor(a!) q, Tensor k, Tensor v, "
                       "Tensor(a!) k_cache, Tensor(a!) v_cache, Tensor start) -> ()",
+    # GGML Q8_0 KV cache: uint8 tensors [B, Hkv, Lmax, head_dim / 32 * 34]
+    "flash_attn_decode_q8": "(Tensor q, Tensor k_cache, Tensor v_cache, Tensor lens, Tensor(a!) out) -> ()",
+    "rope_kv_append_q8": "(int rotary_dim, float freq_base, int style, Tensor(a!) q, Tensor k, Tensor v, "
+                         "Tensor(a!) k_cache, Tensor(a!) v_cache, Tensor start) -> ()",
 }
 _library = torch.library.Library("minfer", "FRAGMENT")
 for _name, _schema in _DEFS.items():
@@ -137,9 +141,31 @@ def _workspace_for(device: torch.device, nbytes: int, cache: dict, stream: int =
     return t
 
 
+def _check_q8_cache(cache: torch.Tensor, batch: int, head_dim: int, what: str) -> None:
+    torch._check(cache.is_cuda and cache.dtype == torch.uint8 and cache.dim() == 4, lambda: f"{what} must be a CUDA uint8 [B, Hkv, Lmax, bytes] tensor")
+    torch._check(cache.size(0) == batch and cache.size(3) == head_dim // 32 * 34, lambda: f"{what}: batch or row bytes do not match (row = head_dim/32 blocks of 34 bytes)")
+    torch._check(cache.stride(3) == 1 and cache.stride(2) == cache.size(3), lambda: f"{what}: rows of one head must be contiguous")
+    torch._check(cache.size(2) % 2 == 0, lambda: f"{what}: the padded length must be even")
+
+
+def _flash_attn_decode_q8_cuda(q, k_cache, v_cache, lens, out) -> None:
+    torch._check(q.is_cuda and out.is_cuda and q.dim() == 4 and out.dim() == 4 and q.shape == out.shape, lambda: "q/out must be CUDA [B, H, 1, D] tensors")
+    torch._check(q.dtype == out.dtype and q.stride(-1) == 1 and out.stride(-1) == 1, lambda: "q/out dtype or innermost stride")
+    torch._check(q.size(2) == 1, lambda: "decode takes one query token per sequence")
+    _check_q8_cache(k_cache, q.size(0), q.size(3), "k_cache")
+    _check_q8_cache(v_cache, q.size(0), q.size(3), "v_cache")
+    torch._check(k_cache.shape == v_cache.shape and k_cache.stride() == v_cache.stride(), lambda: "the caches must share shape and strides")
+    torch._check(q.size(1) % k_cache.size(1) == 0, lambda: "n_heads must be a multiple of n_kv_heads")
+    _decode_call(q, k_cache, v_cache, lens, out, _lib.KV_Q8_0)
+
+
 def _flash_attn_decode_cuda(q, k_cache, v_cache, lens, out) -> None:
     _check_qkv(q, k_cache, v_cache, out)
     torch._check(q.size(2) == 1, lambda: "decode takes one query token per sequence")
+    _decode_call(q, k_cache, v_cache, lens, out, _lib.KV_16BIT)
+
+
+def _decode_call(q, k_cache, v_cache, lens, out, kv_format) -> None:
     torch._check(lens.is_cuda and lens.device == q.device, lambda: "lens must be on the same CUDA device")
     torch._check(lens.dtype == torch.int32 and lens.dim() == 1 and lens.is_contiguous(),
                  lambda: "lens must be a contiguous int32 vector")
@@ -152,13 +178,14 @@ def _flash_attn_decode_cuda(q, k_cache, v_cache, lens, out) -> None:
     p.dtype = _dtype_tag(q)
     p.chunk = 0
     p.softmax_scale = 0.0
+    p.kv_format = kv_format
     for i in range(2):
         p.q_stride[i] = q.stride(i)
         p.out_stride[i] = out.stride(i)
     for i in range(3):
         p.kv_stride[i] = k_cache.stride(i)
     need = _lib.lib.minfer_attn_decode_workspace_bytes(p.batch, p.n_heads, p.max_len, p.head_dim, 0)
-    ws = _workspace_for(q.device, need, _workspace)
+    ws = _workspace_for(q.device, need, _workspace, torch.cuda.current_stream(q.device).cuda_stream)
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
@@ -195,18 +222,27 @@ def _neox_rope_cuda(rotary_dim, start_pos, freq_base, x) -> None:
     _rope_inplace_cuda(1, rotary_dim, start_pos, freq_base, x)
 
 
-def _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start) -> None:
+def _rope_kv_append_q8_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start) -> None:
+    _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start, q8=True)
+
+
+def _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start, q8=False) -> None:
     torch._check(q.is_cuda and k.is_cuda and v.is_cuda and k_cache.is_cuda and v_cache.is_cuda and start.is_cuda,
                  lambda: "all tensors must be on CUDA")
     torch._check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and k_cache.dim() == 4 and v_cache.dim() == 4,
                  lambda: "q/k/v must be [B, L, H, D] and the caches [B, Hkv, Lmax, D]")
-    torch._check(q.dtype == k.dtype == v.dtype == k_cache.dtype == v_cache.dtype, lambda: "dtypes differ")
+    if q8:
+        torch._check(q.dtype == k.dtype == v.dtype, lambda: "dtypes differ")
+        _check_q8_cache(k_cache, q.size(0), q.size(3), "k_cache")
+        _check_q8_cache(v_cache, q.size(0), q.size(3), "v_cache")
+    else:
+        torch._check(q.dtype == k.dtype == v.dtype == k_cache.dtype == v_cache.dtype, lambda: "dtypes differ")
     torch._check(k.shape == v.shape and k.stride() == v.stride(), lambda: "k and v must share shape and strides")
     torch._check(k_cache.shape == v_cache.shape and k_cache.stride() == v_cache.stride(),
                  lambda: "the caches must share shape and strides")
     torch._check(q.size(0) == k.size(0) == k_cache.size(0) and q.size(1) == k.size(1), lambda: "batch / seq mismatch")
-    torch._check(k.size(2) == k_cache.size(1) and q.size(3) == k.size(3) == k_cache.size(3),
-                 lambda: "head count / head_dim mismatch")
+    torch._check(k.size(2) == k_cache.size(1) and q.size(3) == k.size(3), lambda: "head count / head_dim mismatch")
+    torch._check(q8 or k.size(3) == k_cache.size(3), lambda: "head_dim mismatch")
     torch._check(q.stride(-1) == 1 and k.stride(-1) == 1 and k_cache.stride(-1) == 1, lambda: "innermost stride must be 1")
     torch._check(start.dtype == torch.int32 and start.dim() == 1 and start.numel() == q.size(0) and start.is_contiguous(),
                  lambda: "start must be a contiguous int32 vector with one entry per sequence")
@@ -218,12 +254,15 @@ def _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache
     p.batch, p.seq, p.n_heads, p.n_kv_heads, p.head_dim = q.size(0), q.size(1), q.size(2), k.size(2), q.size(3)
     p.rotary_dim, p.start_pos, p.max_len, p.freq_base = rotary_dim, 0, k_cache.size(2), freq_base
     p.dtype, p.style = _dtype_tag(q), style
+    p.cache_format = _lib.KV_Q8_0 if q8 else _lib.KV_16BIT
     _rope_call(p, q.device)
 
 
 _library.impl("il_rope", _il_rope_cuda, "CUDA")
 _library.impl("neox_rope", _neox_rope_cuda, "CUDA")
 _library.impl("rope_kv_append", _rope_kv_append_cuda, "CUDA")
+_library.impl("rope_kv_append_q8", _rope_kv_append_q8_cuda, "CUDA")
+_library.impl("flash_attn_decode_q8", _flash_attn_decode_q8_cuda, "CUDA")
 _library.impl("flash_attn", _flash_attn_cuda, "CUDA")
 _library.impl("flash_attn_causal", _flash_attn_causal_cuda, "CUDA")
 _library.impl("flash_attn_decode", _flash_attn_decode_cuda, "CUDA")
@@ -283,6 +322,37 @@ def rope_kv_append(rotary_dim: int, freq_base: float, style: int, q: torch.Tenso
     style 0 = interleaved (il_rope), 1 = neox.
     """
     return torch.ops.minfer.rope_kv_append.default(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start)
+
+
+def flash_attn_decode_q8(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, lens: torch.Tensor,
+                         out: torch.Tensor):
+    """
+    flash_attn_decode over a GGML Q8_0 KV cache: caches are uint8 [B, n_kv_heads, max_len, D/32*34]
+    (32 int8 + one fp16 scale per block); equals flash_attn_decode on the dequantised cache.
+    """
+    return torch.ops.minfer.flash_attn_decode_q8.default(q, k_cache, v_cache, lens, out)
+
+
+def rope_kv_append_q8(rotary_dim: int, freq_base: float, style: int, q: torch.Tensor, k: torch.Tensor,
+                      v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, start: torch.Tensor):
+    """rope_kv_append into GGML Q8_0 caches: the rows the 16-bit cache would get, quantised block by block."""
+    return torch.ops.minfer.rope_kv_append_q8.default(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start)
+
+
+@torch.library.register_fake("minfer::flash_attn_decode_q8")
+def _(q, k_cache, v_cache, lens, out):
+    torch._check(q.dtype in (torch.float16, torch.bfloat16) and out.dtype == q.dtype)
+    torch._check(k_cache.dtype == torch.uint8 and v_cache.dtype == torch.uint8)
+    torch._check(lens.dtype == torch.int32)
+    torch._check(q.device.type == "cuda")
+
+
+@torch.library.register_fake("minfer::rope_kv_append_q8")
+def _(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start):
+    torch._check(q.dtype in (torch.float16, torch.bfloat16))
+    torch._check(k_cache.dtype == torch.uint8 and v_cache.dtype == torch.uint8)
+    torch._check(start.dtype == torch.int32)
+    torch._check(q.device.type == "cuda")
 
 
 @torch.library.register_fake("minfer::il_rope")

@@ -166,6 +166,101 @@ def neox_rope_reference(x: torch.Tensor, rotary_dim: int, start_pos: int, base_f
     return xf.to(x.dtype)
 
 
+# ---------------------------------------------------------------------------------------------
+# GGML Q8_0 blocks (32 int8 + one fp16 scale = 34 bytes), restated from the reference's codec:
+#   block layout   src/minfer/kernels/torch_ext/csrc/common/types.hpp:141-146
+#   quant_row_q8_0 src/minfer/kernels/torch_ext/csrc/quants/impl.cpp:1169-1193
+#   dequant_row_q8_0 src/minfer/kernels/torch_ext/csrc/quants/impl.cpp:1153-1166
+# The reference's codec compiles from its own source (see Makefile, target _ref); when that build
+# exists, q8_0_*_ref call it and the tests check the restatement against it byte for byte.
+# ---------------------------------------------------------------------------------------------
+def q8_0_quantize(x: torch.Tensor) -> torch.Tensor:
+    """x [..., k] (k % 32 == 0, any float dtype, upcast exactly to fp32) -> uint8 [..., k/32*34]."""
+    xf = x.detach().to("cpu", torch.float32).contiguous().numpy()
+    lead, k = xf.shape[:-1], xf.shape[-1]
+    assert k % 32 == 0
+    blocks = xf.reshape(-1, k // 32, 32)
+    amax = np.abs(blocks).max(axis=-1)
+    d = (amax / np.float32(127.0)).astype(np.float32)
+    with np.errstate(divide="ignore"):
+        inv = np.where(d != 0, np.float32(1.0) / d, np.float32(0.0)).astype(np.float32)
+    scaled = (blocks * inv[..., None]).astype(np.float32)
+    # C roundf: half away from zero
+    q = np.where(scaled >= 0, np.floor(scaled + np.float32(0.5)), np.ceil(scaled - np.float32(0.5))).astype(np.int8)
+    out = np.empty(blocks.shape[:2] + (34,), dtype=np.uint8)
+    out[..., :2] = d.astype(np.float16).view(np.uint8).reshape(d.shape + (2,))
+    out[..., 2:] = q.view(np.uint8)
+    return torch.from_numpy(out.reshape(lead + (k // 32 * 34,)))
+
+
+def q8_0_dequantize(qb: torch.Tensor, dtype=torch.float16) -> torch.Tensor:
+    """uint8 [..., nb*34] -> [..., nb*32] in `dtype`: each value is (dtype)(q * d) with d the block's fp16 scale."""
+    raw = qb.detach().to("cpu").contiguous().numpy()
+    lead = raw.shape[:-1]
+    blocks = raw.reshape(-1, raw.shape[-1] // 34, 34)
+    d = blocks[..., :2].copy().view(np.float16).astype(np.float32)[..., 0]
+    q = blocks[..., 2:].copy().view(np.int8).astype(np.float32)
+    with np.errstate(invalid="ignore", over="ignore"):  # garbage scales (inf/nan) in never-used rows are allowed
+        vals = torch.from_numpy((q * d[..., None]).astype(np.float32)).to(dtype)
+    return vals.reshape(lead + (blocks.shape[1] * 32,))
+
+
+_REF_LIB = os.path.join(_HERE, "_ref", "libminfer_ref_quants.so")
+_ref = None
+
+
+def reference_build_available() -> bool:
+    return os.path.exists(_REF_LIB)
+
+
+def _load_ref():
+    global _ref
+    if _ref is None:
+        lib = ctypes.CDLL(_REF_LIB)
+        lib.ref_quant_row_q8_0.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
+        lib.ref_dequant_row_q8_0_f32.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
+        lib.ref_dequant_row_q8_0_f16.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
+        _ref = lib
+    return _ref
+
+
+def q8_0_quantize_ref(x: torch.Tensor) -> torch.Tensor:
+    """The reference's own quant_row_q8_0 (compiled from its source into oracle/_ref)."""
+    lib = _load_ref()
+    xf = x.detach().to("cpu", torch.float32).contiguous()
+    k = xf.shape[-1]
+    out = torch.empty(xf.shape[:-1] + (k // 32 * 34,), dtype=torch.uint8)
+    lib.ref_quant_row_q8_0(xf.data_ptr(), out.data_ptr(), xf.numel())
+    return out
+
+
+def q8_0_dequantize_ref(qb: torch.Tensor, dtype=torch.float16) -> torch.Tensor:
+    """The reference's own dequant_row_q8_0<float> / <half>."""
+    lib = _load_ref()
+    raw = qb.detach().to("cpu").contiguous()
+    n = raw.numel() // 34 * 32
+    out = torch.empty(raw.shape[:-1] + (raw.shape[-1] // 34 * 32,), dtype=dtype)
+    if dtype == torch.float16:
+        lib.ref_dequant_row_q8_0_f16(raw.data_ptr(), out.data_ptr(), n)
+    else:
+        assert dtype == torch.float32
+        lib.ref_dequant_row_q8_0_f32(raw.data_ptr(), out.data_ptr(), n)
+    return out
+
+
+def build_ref(reference_root: str = "/root/reference") -> bool:
+    """Compile the reference's quant codec from its own sources (only where the reference tree exists)."""
+    src = os.path.join(reference_root, "src", "minfer", "kernels", "torch_ext", "csrc", "quants", "impl.cpp")
+    if not os.path.exists(src):
+        return reference_build_available()
+    rc = subprocess.run(["make", "-C", _HERE, "_ref", f"REFERENCE={reference_root}",
+                         f"TORCH_INCLUDE={os.path.join(os.path.dirname(torch.__file__), 'include')}"],
+                        capture_output=True, text=True)
+    if rc.returncode != 0:
+        raise RuntimeError("building oracle/_ref failed:\n" + rc.stdout + rc.stderr)
+    return True
+
+
 def within_tolerance(actual: torch.Tensor, expected: torch.Tensor, atol: float = 2e-3, rtol: float = 2e-3):
     """allclose with the path's stated tolerance; returns (ok, max_abs_err, n_bad)."""
     a = actual.detach().float().cpu()

@@ -130,6 +130,18 @@ def main():
             out[f"il_{start}"] = bits16(per_token(refs.il_rope, x, rot, start, base))
             out[f"neox_{start}"] = bits16(per_token(refs.neox_rope, x, rot, start, base))
         np.savez(os.path.join(HERE, name + ".npz"), x=bits16(x), rot=np.array(rot), base=np.array(base), **out)
+    # GGML Q8_0: bytes produced by the reference's own quant_row_q8_0 (compiled from its source into
+    # oracle/_ref by `make -C oracle _ref`) and its fp16 dequantisation
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from oracle import oracle as O
+    if O.build_ref(root):
+        g = torch.Generator().manual_seed(41)
+        x = (torch.randn(24, 128, generator=g) * torch.logspace(-3, 2, 24)[:, None]).half()
+        x[3, :32] = 0
+        x[5, 40] = 60000.0
+        qb = O.q8_0_quantize_ref(x.float())
+        np.savez(os.path.join(HERE, "q8_0_rows.npz"), x=bits16(x), q=qb.numpy(),
+                 deq16=bits16(O.q8_0_dequantize_ref(qb, torch.float16)))
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 
