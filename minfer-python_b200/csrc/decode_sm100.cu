@@ -54,23 +54,48 @@ template <bool BF16>
 __device__ __forceinline__ void dequant8(const uint8_t* block, int part, bool live, uint8_t* dst) {
   uint4 out = make_uint4(0u, 0u, 0u, 0u);
   if (live) {
-    const float d = __half2float(*reinterpret_cast<const __half*>(block));
     const uint16_t* q16 = reinterpret_cast<const uint16_t*>(block + 2 + part * 8);  // 2-byte aligned
-    uint32_t w[4];
+    const uint32_t w0 = static_cast<uint32_t>(q16[0]) | (static_cast<uint32_t>(q16[1]) << 16);
+    const uint32_t w1 = static_cast<uint32_t>(q16[2]) | (static_cast<uint32_t>(q16[3]) << 16);
+    if constexpr (BF16) {
+      const float d = __half2float(*reinterpret_cast<const __half*>(block));
+      const uint32_t w[2] = {w0, w1};
+      uint32_t o[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t two = q16[i];
-      const float f0 = static_cast<float>(static_cast<int8_t>(two & 0xFFu)) * d;
-      const float f1 = static_cast<float>(static_cast<int8_t>(two >> 8)) * d;
-      w[i] = pack2<BF16>(f0, f1);
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t two = (w[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu;
+        o[i] = pack2<true>(static_cast<float>(static_cast<int8_t>(two & 0xFFu)) * d,
+                           static_cast<float>(static_cast<int8_t>(two >> 8)) * d);
+      }
+      out = make_uint4(o[0], o[1], o[2], o[3]);
+    } else {
+      // No conversion instructions: the byte q + 128 dropped into the mantissa of the half 1024.0
+      // reads as 1024 + 128 + q; subtracting 1152 leaves q exactly, and one half multiply by d
+      // rounds once, as (half)(q * d) does.
+      const uint32_t dbits = *reinterpret_cast<const uint16_t*>(block);
+      const __half2 d2 = *reinterpret_cast<const __half2*>(&(const uint32_t&)(dbits | (dbits << 16)));
+      const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+      const uint32_t x[2] = {w0 ^ 0x80808080u, w1 ^ 0x80808080u};
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t lo = __byte_perm(x[i], 0x64646464u, 0x5140);  // bytes 0,1 -> two halves 0x64:b
+        const uint32_t hi = __byte_perm(x[i], 0x64646464u, 0x5342);  // bytes 2,3
+        const __half2 qlo = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias);
+        const __half2 qhi = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
+        const __half2 vlo = __hmul2(qlo, d2);
+        const __half2 vhi = __hmul2(qhi, d2);
+        o[2 * i] = *reinterpret_cast<const uint32_t*>(&vlo);
+        o[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&vhi);
+      }
+      out = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    out = make_uint4(w[0], w[1], w[2], w[3]);
   }
   *reinterpret_cast<uint4*>(dst) = out;
 }
 
 template <int D, bool BF16, bool Q8>
-__global__ void __launch_bounds__(kWarps * 32, 2) decode_split_kernel(const DecodeArgs a) {
+__global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(const DecodeArgs a) {
   constexpr int kRowBytes = D * 2;
   constexpr int kTileBytes = kTileKeys * kRowBytes;        // one of K or V, 16-bit
   constexpr int kChunksPerRow = D / 8;                     // 16-byte chunks
@@ -80,9 +105,9 @@ __global__ void __launch_bounds__(kWarps * 32, 2) decode_split_kernel(const Deco
   constexpr int kQTileBytes = kTileKeys * kQRowBytes;      // 2176 (D=128) / 1088 (D=64): multiples of 16
   constexpr int kQChunks = kQTileBytes / 16;
   constexpr int kQLoadsPerLane = (kQChunks + 31) / 32;
-  // per warp: the ring of raw tiles, plus (Q8) one dequantised K and V tile
+  // per warp: the ring of raw tiles, plus (Q8) one 16-bit tile that holds the dequantised K, then V
   constexpr int kRingBytes = kStages * 2 * (Q8 ? kQTileBytes : kTileBytes);
-  constexpr int kWarpBytes = kRingBytes + (Q8 ? 2 * kTileBytes : 0);
+  constexpr int kWarpBytes = kRingBytes + (Q8 ? kTileBytes : 0);
 
   extern __shared__ __align__(128) uint8_t smem[];
 
@@ -193,26 +218,27 @@ __global__ void __launch_bounds__(kWarps * 32, 2) decode_split_kernel(const Deco
 
     const int key0 = c0 + (warp + i * kWarps) * kTileKeys;
     uint32_t sk, sv;
-    if constexpr (Q8) {
-      // dequantise the raw tile into the warp's 16-bit K and V tiles (same swizzle as the 16-bit path)
-      const uint8_t* raw_k = wsm + (i % kStages) * 2 * kQTileBytes;
-      const uint8_t* raw_v = raw_k + kQTileBytes;
-      uint8_t* deq_k = wsm + kRingBytes;
-      uint8_t* deq_v = deq_k + kTileBytes;
-      const int live_rows = min(kTileKeys, c1 - key0);
-      __syncwarp();  // the previous tile's ldmatrix reads of deq_* are done
+    // Q8: dequantise K (and later V) of the raw tile into the warp's one 16-bit tile, same swizzle
+    // as the 16-bit path, so the ldmatrix / mma code below is shared
+    const uint8_t* raw_k = wsm + (Q8 ? (i % kStages) * 2 * kQTileBytes : 0);
+    const int live_rows = min(kTileKeys, c1 - key0);
+    auto dequant_tile = [&](const uint8_t* raw) {
+      uint8_t* deq = wsm + kRingBytes;
+      __syncwarp();  // earlier ldmatrix reads of the tile are done
 #pragma unroll
       for (int t = 0; t < kLoadsPerLane; ++t) {
         const int idx = t * 32 + lane;
         const int row = idx / kChunksPerRow;
         const int chunk = idx % kChunksPerRow;
-        const int off = row * kQRowBytes + (chunk >> 2) * 34;  // the block holding elements 8*chunk .. 8*chunk+7
-        dequant8<BF16>(raw_k + off, chunk & 3, row < live_rows, deq_k + swz<D>(row, chunk));
-        dequant8<BF16>(raw_v + off, chunk & 3, row < live_rows, deq_v + swz<D>(row, chunk));
+        // the block holding elements 8*chunk .. 8*chunk+7 of the row
+        dequant8<BF16>(raw + row * kQRowBytes + (chunk >> 2) * 34, chunk & 3, row < live_rows, deq + swz<D>(row, chunk));
       }
       __syncwarp();
+    };
+    if constexpr (Q8) {
+      dequant_tile(raw_k);
       sk = wsm_u32 + kRingBytes;
-      sv = sk + kTileBytes;
+      sv = sk;
     } else {
       sk = wsm_u32 + (i % kStages) * 2 * kTileBytes;
       sv = sk + kTileBytes;
@@ -277,6 +303,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) decode_split_kernel(const Deco
     pa[3] = pack2<BF16>(sacc[1][2], sacc[1][3]);
 
     // ---- O[16 heads x D] += P V ----
+    if constexpr (Q8) dequant_tile(raw_k + kQTileBytes);
 #pragma unroll
     for (int dn = 0; dn < D / 16; ++dn) {
       uint32_t r0, r1, r2, r3;
@@ -368,7 +395,7 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
 template <int D, bool BF16, bool Q8>
 cudaError_t launch_one(const DecodeArgs& a, cudaStream_t stream) {
   constexpr int kRaw = Q8 ? kTileKeys * (D / 32) * 34 : kTileKeys * D * 2;
-  constexpr int smem = kWarps * (kStages * 2 * kRaw + (Q8 ? 2 * kTileKeys * D * 2 : 0));
+  constexpr int smem = kWarps * (kStages * 2 * kRaw + (Q8 ? kTileKeys * D * 2 : 0));
   static_assert(smem / kWarps >= 16 * D * 4 + 128, "the per-warp region also holds the fp32 merge buffer");
   static bool attr_done[64] = {};
   int dev = 0;
