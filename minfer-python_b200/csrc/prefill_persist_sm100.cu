@@ -131,7 +131,10 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                        const __grid_constant__ CUtensorMap tm_v, const PrefillArgs a) {
   constexpr int kDB = D / 64;
   constexpr int kTileBytes = kDB * kBlockBytes;
-  constexpr int kStages = (D == 128) ? 4 : 8;
+#ifndef MINFER_ATTN_STAGES128
+#define MINFER_ATTN_STAGES128 4
+#endif
+  constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
   constexpr int kKvEmpty = kKvFull + kStages;
   constexpr int kNumBars = kKvFull + 2 * kStages;
   constexpr uint32_t kTmemCols = 512;
@@ -529,7 +532,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 template <int D, bool BF16>
 cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, PrefillArgs a,
                                cudaStream_t stream) {
-  constexpr int kStages = (D == 128) ? 4 : 8;
+  constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
   constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 512 + 1024;
   static bool attr_done[64] = {};
   static int sm_count[64] = {};
