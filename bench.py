@@ -323,7 +323,7 @@ def run_gpu_arm(args):
                          "frac": per_gpu_tflops / tensor_peak, "traffic": traffic.get("prefill"),
                          "peak_source": f"{peaks['source']}, {peak_kind} bf16 matmul figure",
                          "frac_of_nominal_2250": per_gpu_tflops / 2250.0,
-                         "kernel": "prefill_ws_kernel<128,f16>"},
+                         "kernel": "prefill_persist_kernel<128,f16>"},
             "decode": {"value": dec_gbs * world, "unit": "GB/s", "ms_per_step": ms_dec,
                        "workload": "config3: B=64/GPU Hq=32 Hkv=8 D=128, lens U[512,8192] seed 2, cache padded to 8192",
                        "bytes_per_step": dec_bytes, "gpu_launches_per_step": 2,

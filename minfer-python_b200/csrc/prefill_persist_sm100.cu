@@ -42,9 +42,12 @@ constexpr int kRegsSoftmax = 216;
 constexpr int kRegsOther = 72;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 #ifndef MINFER_ATTN_POLY_OF_8
-#define MINFER_ATTN_POLY_OF_8 2
+#define MINFER_ATTN_POLY_OF_8 0
 #endif
-constexpr int kPolyOf8 = MINFER_ATTN_POLY_OF_8;  // share of exp2 evaluations done without the SFU
+// Share (of 8) of the exp2 evaluations done with a cubic on the FMA pipes instead of the special-function
+// unit.  2 gains ~3 % in a short burst at full clock, but the extra instructions cost ~1.5 % once the
+// 1 kW power cap holds the clock down, which is where a sustained run lives: off by default.
+constexpr int kPolyOf8 = MINFER_ATTN_POLY_OF_8;
 
 // barrier indices ([2] = one per slot)
 constexpr int kQFull = 0;

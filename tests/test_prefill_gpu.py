@@ -143,6 +143,51 @@ def test_simple_kernel_flag_agrees(kerns):
         check_close(out, want, f"flags={flags}")
 
 
+@pytest.mark.parametrize("Lq,Lk,H,Hkv,D", [(200, 712, 4, 2, 128), (1, 300, 3, 3, 64), (384, 385, 8, 1, 128)])
+def test_causal_with_more_keys_than_queries(kerns, Lq, Lk, H, Hkv, D):
+    """Chunked prefill: the queries are the LAST Lq positions of a length-Lk sequence (key j visible to
+    query i iff j <= i + Lk - Lq)."""
+    g = torch.Generator().manual_seed(Lq + Lk)
+    q = torch.randn(2, H, Lq, D, generator=g).half()
+    k = torch.randn(2, Hkv, Lk, D, generator=g).half()
+    v = torch.randn(2, Hkv, Lk, D, generator=g).half()
+    want = O.attention_f64(q, k, v, causal=True)
+    check_close(run_causal(kerns, q, k, v), want, f"Lq={Lq} Lk={Lk}")
+
+
+def test_explicit_softmax_scale_through_the_c_abi():
+    import ctypes
+    from minfer.kernels.torch_ext import _lib
+    B, H, Hkv, L, D, scale = 1, 4, 2, 300, 128, 0.05
+    q, k, v = seeded_qkv(91, B, H, Hkv, L, L, D, torch.float16)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    out = torch.full((B, H, L, D), float("nan"), dtype=torch.float16, device="cuda")
+    p = _lib.PrefillParams()
+    p.q, p.k, p.v, p.out = qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr()
+    for i in range(3):
+        p.q_stride[i], p.kv_stride[i], p.out_stride[i] = qd.stride(i), kd.stride(i), out.stride(i)
+    p.batch, p.n_heads, p.n_kv_heads, p.seq_q, p.seq_k, p.head_dim = B, H, Hkv, L, L, D
+    p.dtype, p.causal, p.softmax_scale, p.flags = _lib.F16, 1, scale, 0
+    assert _lib.lib.minfer_attn_prefill(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+    torch.cuda.synchronize()
+    check_close(out, O.attention_f64(q, k, v, causal=True, scale=scale), "explicit scale")
+
+
+def test_adversarial_score_growth(kerns):
+    """Scores that grow by far more than 2^8 from one key tile to the next force the reference maximum to
+    move (and O to be rescaled) on every tile; and a huge early outlier must not poison later tiles."""
+    B, H, Hkv, L, D = 1, 2, 1, 640, 128
+    g = torch.Generator().manual_seed(17)
+    q = torch.randn(B, H, L, D, generator=g).half()
+    k = torch.randn(B, Hkv, L, D, generator=g).half()
+    v = torch.randn(B, Hkv, L, D, generator=g).half()
+    k *= (1 + torch.arange(L) // 128 * 6).view(1, 1, L, 1).half()      # later key tiles score much higher
+    k[0, 0, 3] *= 40                                                    # an early outlier
+    want = O.attention_f64(q, k, v, causal=True)
+    check_close(run_causal(kerns, q, k, v), want, "growing scores")
+    check_close(run_masked(kerns, q, k, v, O.causal_mask(B, L)), want, "growing scores, dense mask")
+
+
 def test_bf16_medium(kerns):
     q, k, v = seeded_qkv(7, 1, 8, 1, 1024, 1024, 128, torch.bfloat16)
     want = O.prefill_oracle(q, k, v, causal=True)
