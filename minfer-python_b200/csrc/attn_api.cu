@@ -44,9 +44,9 @@ int check_device() {
 // Tensor map over a [batch, heads, rows, head_dim] 16-bit tensor with element
 // strides (s_b, s_h, s_r, 1).  The three outer dimensions are ordered by
 // ascending stride; pos[] receives the coordinate slot (1..3) of batch, head
-// and row.  Box = 64 elements x 128 rows, 128-byte swizzle, zero fill.
+// and row.  Box = 64 elements x box_rows rows, 128-byte swizzle, zero fill.
 int make_tensor_map(CUtensorMap* tm, const void* base, bool bf16, int head_dim, int64_t batch, int64_t heads,
-                    int64_t rows, const int64_t stride[3], int32_t pos[3]) {
+                    int64_t rows, const int64_t stride[3], int32_t pos[3], int box_rows = 128) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return MINFER_ATTN_ECUDA;
   struct Dim {
@@ -68,7 +68,7 @@ int make_tensor_map(CUtensorMap* tm, const void* base, bool bf16, int head_dim, 
     gdim[i + 1] = static_cast<cuuint64_t>(dims[i].size);
     gstr[i] = static_cast<cuuint64_t>(dims[i].stride) * 2;
     pos[dims[i].which] = i + 1;
-    if (dims[i].which == 2) box[i + 1] = 128;
+    if (dims[i].which == 2) box[i + 1] = static_cast<cuuint32_t>(box_rows);
   }
   CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                    const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -153,6 +153,11 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
   rc = make_tensor_map(&tv, p->v, bf16, p->head_dim, p->batch, p->n_kv_heads, p->seq_k, p->kv_stride, vpos);
   if (rc != MINFER_ATTN_OK) return rc;
 
+  // output map of the persistent kernel's epilogue: one softmax warp stores 32 rows x 64 columns at a time
+  alignas(64) CUtensorMap to;
+  rc = make_tensor_map(&to, p->out, bf16, p->head_dim, p->batch, p->n_heads, p->seq_q, p->out_stride, a.out_pos, 32);
+  if (rc != MINFER_ATTN_OK) return rc;
+
   a.out = p->out;
   a.mask = p->causal ? nullptr : p->mask;
   a.cls = nullptr;
@@ -188,7 +193,7 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
   if (p->flags & MINFER_ATTN_FLAG_SIMPLE_KERNEL) e = launch_prefill(tq, tk, tv, a, p->head_dim, bf16, st);
   else if (a.mask != nullptr || (p->flags & MINFER_ATTN_FLAG_ONE_ITEM_PER_CTA))
     e = launch_prefill_ws(tq, tk, tv, a, p->head_dim, bf16, st);
-  else e = launch_prefill_persist(tq, tk, tv, a, p->head_dim, bf16, st);
+  else e = launch_prefill_persist(tq, tk, tv, to, a, p->head_dim, bf16, st);
   return cuda_result(e);
 }
 

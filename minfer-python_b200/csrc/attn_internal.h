@@ -31,13 +31,14 @@ struct PrefillArgs {
   // map; coordinate 0 is always head_dim
   int32_t q_pos[3];
   int32_t kv_pos[3];
+  int32_t out_pos[3];  // coordinate slots of the output tensor map (persistent kernel only)
 };
 
 size_t prefill_smem_bytes(int head_dim);
 cudaError_t launch_prefill_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                               const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream);
 cudaError_t launch_prefill_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                                   const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream);
+                                   const CUtensorMap& to, const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream);
 cudaError_t launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillArgs& a,
                            int head_dim, bool bf16, cudaStream_t stream);
 

@@ -26,6 +26,14 @@
 //   q_empty[s]  MMA -> TMA      last S MMA of the item has read Q_s
 //   o_free[s]   softmax -> MMA  the epilogue has copied O_s out of tensor memory
 // The K/V ring simply continues across items.
+//
+// Two more differences from the one-item kernel.  P is handed to the MMA warp in
+// pieces (p_full[s][piece], one barrier per piece), so the PV MMAs of the first
+// half of a key tile run while the second half's exponentials are still being
+// computed, and only the last piece's MMAs and the next S stay on the slot's
+// critical path.  And the output leaves through the TMA unit: each softmax warp
+// packs its 32 rows, 64 columns at a time, into 4 KB of swizzled shared memory and
+// one lane issues a tensor store, instead of every thread storing its own row.
 #include "attn_internal.h"
 #include "ptx.cuh"
 
@@ -36,10 +44,11 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kTileN = 128;
 constexpr int kBlockBytes = 128 * 128;
+constexpr int kEpiBytes = 32 * 128;  // 32 rows x 64 columns of 16-bit output per softmax warp
 constexpr int kThreads = 384;  // softmax 0 (warps 0-3), softmax 1 (4-7), MMA (8), TMA (9), 2 idle warps
-// setmaxnreg split of the 384 x 168 launch allocation: 8 x 216 + 4 x 72 = 12 x 168
-constexpr int kRegsSoftmax = 216;
-constexpr int kRegsOther = 72;
+// setmaxnreg split of the 384 x 168 launch allocation: 8 x 208 + 4 x 88 = 12 x 168
+constexpr int kRegsSoftmax = 208;
+constexpr int kRegsOther = 88;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 #ifndef MINFER_ATTN_POLY_OF_8
 #define MINFER_ATTN_POLY_OF_8 0
@@ -48,17 +57,36 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 // unit.  2 gains ~3 % in a short burst at full clock, but the extra instructions cost ~1.5 % once the
 // 1 kW power cap holds the clock down, which is where a sustained run lives: off by default.
 constexpr int kPolyOf8 = MINFER_ATTN_POLY_OF_8;
+#ifndef MINFER_ATTN_P_CHUNKS
+#define MINFER_ATTN_P_CHUNKS 2
+#endif
+// P is published to the MMA warp in this many pieces per key tile (1, 2 or 4): with more than one, the PV
+// MMAs of the early pieces run under the rest of the exponentials, and only the last piece's MMAs and the
+// next S stay on the slot's critical path.
+constexpr int kPChunks = MINFER_ATTN_P_CHUNKS;
+static_assert(kPChunks == 1 || kPChunks == 2 || kPChunks == 4, "P is written as four 32-key pieces");
 
 // barrier indices ([2] = one per slot)
 constexpr int kQFull = 0;
 constexpr int kQEmpty = 2;
 constexpr int kSFull = 4;
-constexpr int kPFull = 6;
+constexpr int kPFull = 16;   // [2 slots][4 pieces]: one barrier per piece, so a fast thread's next piece cannot complete a phase early
 constexpr int kODone = 8;
 constexpr int kOFree = 10;
 constexpr int kSched = 12;   // [kSchedRing] item published by the TMA warp
 constexpr int kSchedRing = 4; // the TMA warp is never more than two items ahead of the slowest role
-constexpr int kKvFull = 16;  // [kStages], then kKvEmpty [kStages]
+constexpr int kKvFull = 24;  // [kStages], then kKvEmpty [kStages]
+
+// Optional accounting for tuning (compiled in only with -DMINFER_ATTN_TRACE): thread 0 of every CTA
+// (slot 0, row 0) sums where its clocks went and writes 8 words behind the 16 status words.
+#ifdef MINFER_ATTN_TRACE
+#define P_ACC(stmt) do { if (acc_on) { stmt; } } while (0)
+// timeline of CTA 0's first item: role r, tile j, event e -> clock64()
+#define P_TL(r, jj, e) do { if (tl_on && k == 0 && (jj) < 64) tl_buf[((r) * 64 + (jj)) * 12 + (e)] = clock64(); } while (0)
+#else
+#define P_ACC(stmt) do { } while (0)
+#define P_TL(r, jj, e) do { } while (0)
+#endif
 
 __device__ __forceinline__ void report_p(int32_t* status, int site) {
   if (status != nullptr && atomicCAS(status, 0, kStatusWaitTimeout) == 0) {
@@ -131,7 +159,8 @@ __device__ __forceinline__ int item_id(int k, int n_items) {
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                       const __grid_constant__ CUtensorMap tm_v, const PrefillArgs a) {
+                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                       const PrefillArgs a) {
   constexpr int kDB = D / 64;
   constexpr int kTileBytes = kDB * kBlockBytes;
 #ifndef MINFER_ATTN_STAGES128
@@ -148,7 +177,8 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* s_q = smem;                   // [2][kTileBytes]
   uint8_t* s_kv = s_q + 2 * kTileBytes;  // [kStages][kTileBytes]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_kv + kStages * kTileBytes);
+  uint8_t* s_epi = s_kv + kStages * kTileBytes;  // [8 softmax warps][kEpiBytes] transposing buffers of the epilogue
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_epi + 8 * kEpiBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* sched_id = reinterpret_cast<volatile int*>(tmem_slot + 4);  // [kSchedRing]
@@ -157,6 +187,11 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int warp = tid >> 5;
   const int n_items = a.items_x * a.items_y * a.batch;
   const bool dynamic = a.counter != nullptr;
+#ifdef MINFER_ATTN_TRACE
+  const bool tl_on = a.status != nullptr && blockIdx.x == 0 && (tid & 31) == 0;
+  long long* tl_buf = reinterpret_cast<long long*>(a.status + 16) + 148 * 2 * 12;
+  const int tl_role = warp == 0 ? 0 : warp == 4 ? 1 : warp == 1 ? 2 : 4;  // other softmax warps write to a dump row
+#endif
   // k-th item of this CTA as seen by a consumer role (MMA, softmax): from the ring
   // when items are claimed dynamically, else by the static rule; -1 = no more
   auto next_item = [&](int k, bool& ok) -> int {
@@ -170,7 +205,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_init(&bars[kQFull + i], 1);
       mbar_init(&bars[kQEmpty + i], 1);
       mbar_init(&bars[kSFull + i], 1);
-      mbar_init(&bars[kPFull + i], 128);
+      for (int c = 0; c < 4; ++c) mbar_init(&bars[kPFull + 4 * i + c], 128);
       mbar_init(&bars[kODone + i], 1);
       mbar_init(&bars[kOFree + i], 128);
     }
@@ -305,15 +340,21 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         if (leader) umma_commit(&bars[kSFull + s]);
       };
-      auto issue_pv = [&](int s, uint32_t st, bool accumulate) {
+      // piece c of kPChunks of O_s (+)= P_s * V(stage st); the last piece signals o_done
+      auto issue_pv = [&](int s, uint32_t st, int c, bool accumulate) {
+        constexpr int kSteps = kTileN / 16 / kPChunks;
         const uint32_t va = v_lo + st * (kTileBytes >> 4);
         const uint32_t tp = tmem_base + s * kTileN;  // P: packed 16-bit pairs, 8 columns per 16 keys
         const uint32_t to = tmem_base + 256 + s * 128;
-        if (leader) umma_ts(to, tp, desc(va, kHi), kIdescO, accumulate ? 1u : 0u);
 #pragma unroll
-        for (int kk = 1; kk < kTileN / 16; ++kk)
-          if (leader) umma_ts_acc(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO);
-        if (leader) umma_commit(&bars[kODone + s]);
+        for (int i = 0; i < kSteps; ++i) {
+          const int kk = c * kSteps + i;
+          if (leader) {
+            if (i == 0) umma_ts(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO, accumulate ? 1u : 0u);
+            else umma_ts_acc(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO);
+          }
+        }
+        if (c == kPChunks - 1 && leader) umma_commit(&bars[kODone + s]);
       };
 
       uint32_t tiles[2] = {0u, 0u};  // key tiles finished per slot (parity of p_full)
@@ -357,9 +398,17 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
               // O_s still holds the previous item's result until its epilogue has read it
               if (!(ok = mbar_wait(&bars[kOFree + s], (items[s] - 1) & 1u, abort_flag))) { report_p(a.status, 35); continue; }
             }
-            if (!(ok = mbar_wait(&bars[kPFull + s], tiles[s] & 1u, abort_flag))) { report_p(a.status, 33); continue; }
-            tc_fence_after();
-            issue_pv(s, stv, j > 0);
+            P_TL(3, j, s * 6 + 0);
+#pragma unroll
+            for (int c = 0; c < kPChunks; ++c) {
+              if (!ok) continue;
+              if (!(ok = mbar_wait(&bars[kPFull + 4 * s + c], tiles[s] & 1u, abort_flag))) { report_p(a.status, 33); continue; }
+              tc_fence_after();
+              P_TL(3, j, s * 6 + 1 + 2 * (c & 1));
+              issue_pv(s, stv, c, j > 0 || c > 0);
+              P_TL(3, j, s * 6 + 2 + 2 * (c & 1));
+            }
+            if (!ok) continue;
             ++tiles[s];
             if (j + 1 < it.n[s]) {
               if (!k_waited) {
@@ -368,6 +417,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 tc_fence_after();
               }
               issue_s(s, stk);
+              P_TL(3, j, s * 6 + 5);
               if (j + 2 == it.n[s] && leader) umma_commit(&bars[kQEmpty + s]);  // last S of the item for this slot
             }
           }
@@ -398,9 +448,15 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int off = a.seq_k - a.seq_q;
     bool ok = true;
     uint32_t jt = 0;  // key tiles this slot has processed over the CTA's lifetime
+#ifdef MINFER_ATTN_TRACE
+    const bool acc_on = a.status != nullptr && (tid & 127) == 0;
+    long long acc_t0 = clock64(), acc_c = 0, acc_first = 0, acc_wait = 0, acc_epi = 0, acc_sched = 0, acc_items = 0, acc_ld = 0, acc_max = 0, acc_exp = 0, acc_resc = 0, acc_c2 = 0, acc_ew = 0, acc_el = 0;
+#endif
 
     for (int k = 0; ok; ++k) {
+      P_ACC(acc_c = clock64());
       const int id = next_item(k, ok);
+      P_ACC(acc_sched += clock64() - acc_c);
       if (!ok) { report_p(a.status, 43); break; }
       if (id < 0) break;
       const Item it = decode_item(a, id, dynamic && a.order_by_kv_set);
@@ -414,14 +470,21 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
       for (int j = 0; j < nt; ++j, ++jt) {
         const int kv0 = j * kTileN;
+        P_ACC(acc_c = clock64());
+        P_TL(tl_role, j, 0);
         if (!(ok = mbar_wait(&bars[kSFull + s], jt & 1u, abort_flag))) { report_p(a.status, 40); break; }
+        P_TL(tl_role, j, 1);
+        P_ACC(acc_c2 = clock64(); if (j == 0) acc_first += acc_c2 - acc_c; else acc_wait += acc_c2 - acc_c);
         tc_fence_after();
 
         uint32_t sr[kTileN];
 #pragma unroll
         for (int c = 0; c < kTileN / 32; ++c)
           tmem_ld32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
+        P_TL(tl_role, j, 2);
         tc_wait_ld();
+        P_TL(tl_role, j, 3);
+        P_ACC(acc_c = clock64(); acc_ld += acc_c - acc_c2);
 
         // ---- masking: only the diagonal and the ragged last tile need it ----
         const bool tail = kv0 + kTileN > a.seq_k;
@@ -449,6 +512,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           if (move) m_ref = mx;
           l_run *= alpha;
           if (j > 0) {
+            P_ACC(++acc_resc);
             // PV(j-1) of this slot must have landed before O is touched
             if (!(ok = mbar_wait(&bars[kODone + s], (jt - 1) & 1u, abort_flag))) { report_p(a.status, 41); break; }
             tc_fence_after();
@@ -464,6 +528,8 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           }
         }
 
+        P_TL(tl_role, j, 4);
+        P_ACC(acc_c2 = clock64(); acc_max += acc_c2 - acc_c);
         // ---- P = exp2(S*c - m*c) -> 16-bit pairs -> tensor memory (over S) ----
         const float mb = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
         const float2 sl2_2 = make_float2(sl2, sl2);
@@ -489,39 +555,76 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             pk[e] = pack2<BF16>(p.x, p.y);
           }
           tmem_st16(tmem_s + c * 16, pk);
+          P_TL(tl_role, j, 5 + c);
+          if ((c + 1) % (4 / kPChunks) == 0) {
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars[kPFull + 4 * s + (c + 1) * kPChunks / 4 - 1]);
+            P_TL(tl_role, j, c == 3 ? 10 : 9);
+          }
         }
         l_run += sum2.x + sum2.y;
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(&bars[kPFull + s]);
+        P_ACC(acc_exp += clock64() - acc_c2);
       }
       if (!ok) break;
 
       // ---- epilogue: copy O out of tensor memory, release it, then write O / l ----
+      P_ACC(acc_c = clock64(); ++acc_items);
       if (!(ok = mbar_wait(&bars[kODone + s], (jt - 1) & 1u, abort_flag))) { report_p(a.status, 42); break; }
+      P_ACC(acc_c2 = clock64(); acc_ew += acc_c2 - acc_c);
       tc_fence_after();
       const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
-      uint32_t ow[D / 2];  // the row as packed 16-bit pairs
+      // A thread owns one row of O, but a row-per-thread store would touch 32 cache lines per
+      // instruction and hold the warp behind the SM's store path.  Instead each warp packs 64 columns of
+      // its 32 rows into its own 4 KB of shared memory (16-byte chunks XOR-swizzled by row, the layout of
+      // a 128-byte-swizzled tensor map) and one lane hands the box to the TMA unit; rows past seq_q are
+      // clipped by the tensor map.
+      {
+        const int lane = tid & 31;
+        const uint32_t stage = smem_u32(s_epi + warp * kEpiBytes);
+        const int row0 = q0s + (warp & 3) * 32;  // first row of this warp
+        auto pick = [&](int i) { return a.out_pos[0] == i ? it.b : (a.out_pos[1] == i ? heads : row0); };
+        const int c1 = pick(1), c2 = pick(2), c3 = pick(3);
+        uint32_t o[D];
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tmem_o + c * 32, o);
+        for (int c = 0; c < D / 32; ++c) tmem_ld32(tmem_o + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[c * 32]));
         tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&bars[kOFree + s]);  // the MMA warp may overwrite O_s for the next item
+        P_ACC(acc_el += clock64() - acc_c2);
 #pragma unroll
-        for (int e = 0; e < 16; ++e)
-          ow[c * 16 + e] = pack2<BF16>(__uint_as_float(o[2 * e]) * inv, __uint_as_float(o[2 * e + 1]) * inv);
-      }
-      tc_fence_before();
-      mbar_arrive(&bars[kOFree + s]);  // the MMA warp may overwrite O_s for the next item
-      if (r_glob < a.seq_q) {
-        uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) +
-                        2 * (static_cast<size_t>(it.b) * a.out_stride[0] + static_cast<size_t>(heads) * a.out_stride[1] +
-                             static_cast<size_t>(r_glob) * a.out_stride[2]);
+        for (int h = 0; h < D / 64; ++h) {
+          // the staging buffer is free once the previous box (this pass's predecessor, or the last
+          // one of the previous item) has been read by the TMA unit
+          if (lane == 0) bulk_wait_read();
+          __syncwarp();
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c)
-          *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(ow[c * 4], ow[c * 4 + 1], ow[c * 4 + 2], ow[c * 4 + 3]);
+          for (int c = 0; c < 8; ++c) {
+            uint32_t v[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              v[e] = pack2<BF16>(__uint_as_float(o[h * 64 + c * 8 + 2 * e]) * inv,
+                                 __uint_as_float(o[h * 64 + c * 8 + 2 * e + 1]) * inv);
+            st_shared_v4(stage + lane * 128 + ((c ^ (lane & 7)) << 4), v[0], v[1], v[2], v[3]);
+          }
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA unit
+          __syncwarp();
+          if (lane == 0 && row0 < a.seq_q) {
+            tma_store_4d(&tm_o, stage, h * 64, c1, c2, c3);
+            bulk_commit();
+          }
+        }
       }
+      P_ACC(acc_epi += clock64() - acc_c);
     }
+    if ((tid & 31) == 0) bulk_wait_all();  // the staging buffers stay allocated until the last box has left
+#ifdef MINFER_ATTN_TRACE
+    if (acc_on) {
+      long long* w = reinterpret_cast<long long*>(a.status + 16) + (blockIdx.x * 2 + s) * 12;
+      w[0] = clock64() - acc_t0; w[1] = acc_first; w[2] = acc_wait; w[3] = acc_epi;
+      w[4] = acc_sched; w[5] = acc_items; w[6] = jt; w[7] = acc_ld; w[8] = acc_max; w[9] = acc_exp; w[10] = acc_resc; w[11] = (acc_ew << 32) | acc_el;
+    }
+#endif
   }
 
   tc_fence_before();
@@ -533,10 +636,11 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 }
 
 template <int D, bool BF16>
-cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, PrefillArgs a,
+cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                               const CUtensorMap& to, PrefillArgs a,
                                cudaStream_t stream) {
   constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
-  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 512 + 1024;
+  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 8 * kEpiBytes + 512 + 1024;
   static bool attr_done[64] = {};
   static int sm_count[64] = {};
   int dev = 0;
@@ -566,17 +670,17 @@ cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, con
     e = cudaMemsetAsync(a.counter, 0, sizeof(int), stream);
     if (e != cudaSuccess) return e;
   }
-  prefill_persist_kernel<D, BF16><<<grid, kThreads, smem, stream>>>(tq, tk, tv, a);
+  prefill_persist_kernel<D, BF16><<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, a);
   return cudaGetLastError();
 }
 
 }  // namespace
 
 cudaError_t launch_prefill_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                                   const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream) {
+                                   const CUtensorMap& to, const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream) {
   if (head_dim == 128)
-    return bf16 ? launch_persist_one<128, true>(tq, tk, tv, a, stream) : launch_persist_one<128, false>(tq, tk, tv, a, stream);
-  return bf16 ? launch_persist_one<64, true>(tq, tk, tv, a, stream) : launch_persist_one<64, false>(tq, tk, tv, a, stream);
+    return bf16 ? launch_persist_one<128, true>(tq, tk, tv, to, a, stream) : launch_persist_one<128, false>(tq, tk, tv, to, a, stream);
+  return bf16 ? launch_persist_one<64, true>(tq, tk, tv, to, a, stream) : launch_persist_one<64, false>(tq, tk, tv, to, a, stream);
 }
 
 }  // namespace minfer_attn
