@@ -111,17 +111,18 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* params, void* stream);
 
 /*
  * Optional scratch of a prefill call (device memory, 16-byte aligned).
- * Dense mask: when `workspace` holds at least this many bytes, one pass over the
- * mask classifies its 128 x 128 tiles (nothing visible / everything visible /
- * mixed); the attention kernel then skips tiles nobody can see and reads mask
- * bytes only for mixed ones, so a dense causal or sliding-window mask costs about
- * what the structure it encodes costs.  Without it every tile is visited and
- * masked byte by byte.  Causal / unmasked calls: the first 4 bytes serve as a
- * counter from which the persistent thread blocks claim work items (zeroed by the
- * call on `stream`); without it the items are dealt out in a fixed order.  The
- * result is the same with or without a workspace, only the time differs.  Calls
- * that may overlap on the GPU need separate workspaces.  Returns 0 for invalid
- * sizes, else at least 16.
+ * The first 4 bytes serve as a counter from which the persistent thread blocks
+ * claim work items (zeroed by the call on `stream`); 16 bytes are enough for a
+ * causal / unmasked call, and without them the items are dealt out in a fixed
+ * order.  Dense mask: when `workspace` holds at least the number of bytes returned
+ * here, one pass over the mask classifies its 128 x 128 tiles (nothing visible /
+ * everything visible / mixed) into the bytes after the counter; the attention
+ * kernel then skips tiles nobody can see and reads mask bytes only for mixed
+ * ones, so a dense causal or sliding-window mask costs about what the structure
+ * it encodes costs.  Without it every tile is visited and masked byte by byte.
+ * The result is the same with or without a workspace, only the time differs.
+ * Calls that may overlap on the GPU need separate workspaces.  Returns 0 for
+ * invalid sizes, else 16 + one byte per mask tile.
  */
 size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t seq_k);
 

@@ -162,16 +162,17 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
   a.mask = p->causal ? nullptr : p->mask;
   a.cls = nullptr;
   a.counter = nullptr;
-  // causal / unmasked calls: the first word of a (16-byte aligned) workspace is the work-item counter
-  if (a.mask == nullptr && p->workspace != nullptr && p->workspace_bytes >= 16 && aligned16(p->workspace))
+  // the first word of a (16-byte aligned) workspace is the work-item counter of the persistent kernel;
+  // the tile classes of a dense mask follow at byte 16
+  if (p->workspace != nullptr && p->workspace_bytes >= 16 && aligned16(p->workspace))
     a.counter = static_cast<int*>(p->workspace);
   if (a.mask != nullptr) {
     const size_t need = minfer_attn_prefill_workspace_bytes(p->batch, p->seq_q, p->seq_k);
-    if (p->workspace != nullptr && p->workspace_bytes >= need && !(p->flags & MINFER_ATTN_FLAG_SIMPLE_KERNEL)) {
-      cudaError_t ce = launch_mask_classify(a.mask, static_cast<uint8_t*>(p->workspace), p->batch, p->seq_q, p->seq_k,
-                                            static_cast<cudaStream_t>(stream));
+    if (a.counter != nullptr && p->workspace_bytes >= need && !(p->flags & MINFER_ATTN_FLAG_SIMPLE_KERNEL)) {
+      uint8_t* cls = static_cast<uint8_t*>(p->workspace) + 16;
+      cudaError_t ce = launch_mask_classify(a.mask, cls, p->batch, p->seq_q, p->seq_k, static_cast<cudaStream_t>(stream));
       if (ce != cudaSuccess) return cuda_result(ce);
-      a.cls = static_cast<const uint8_t*>(p->workspace);
+      a.cls = cls;
     }
   }
   a.status = p->status;
@@ -191,7 +192,7 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (p->flags & MINFER_ATTN_FLAG_SIMPLE_KERNEL) e = launch_prefill(tq, tk, tv, a, p->head_dim, bf16, st);
-  else if (a.mask != nullptr || (p->flags & MINFER_ATTN_FLAG_ONE_ITEM_PER_CTA))
+  else if (p->flags & MINFER_ATTN_FLAG_ONE_ITEM_PER_CTA)
     e = launch_prefill_ws(tq, tk, tv, a, p->head_dim, bf16, st);
   else e = launch_prefill_persist(tq, tk, tv, to, a, p->head_dim, bf16, st);
   return cuda_result(e);
@@ -200,7 +201,7 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
 size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t seq_k) {
   if (batch <= 0 || seq_q <= 0 || seq_k <= 0) return 0;
   const size_t cls = static_cast<size_t>(batch) * ((seq_q + 127) / 128) * ((seq_k + 127) / 128);
-  return cls < 16 ? 16 : cls;  // at least the work-item counter of causal calls
+  return 16 + cls;  // the work-item counter, then the tile classes of a dense mask
 }
 
 int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {

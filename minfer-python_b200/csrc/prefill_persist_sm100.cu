@@ -1,7 +1,7 @@
-// Persistent form of the two-tile prefill kernel for causal / unmasked calls.
+// Persistent form of the two-tile prefill kernel: causal, unmasked and dense-mask calls.
 //
 // Same roles, tensor-memory layout and MMA issue order as prefill_ws_sm100.cu
-// (which remains the kernel for dense masks), but one CTA per SM walks a list of
+// (the one-item-per-CTA form kept for cross-checking), but one CTA per SM walks a list of
 // work items instead of exiting after one.  What that buys: tensor memory and the
 // barriers are set up once; the TMA warp already streams the next item's Q/K/V
 // while the softmax warps write the previous item's output; and the MMA warp
@@ -20,6 +20,11 @@
 // shared-memory ring to the other roles.  Without a workspace CTA c takes items
 // c, 2G-1-c, 2G+c, ... (a snake over rounds of G = gridDim.x items), which gives
 // every CTA the same mix of long and short items without any global state.
+//
+// Dense masks (kMasked): the scheduler warp also compacts the item's tile classes into a
+// visit list that travels with the item through the ring, so every role skips the key
+// tiles nobody can see; sched_free[entry] (all consumer roles have left the item) guards
+// the reuse of a ring entry.
 //
 // Hand-offs between items, per slot s (all counted over the CTA's lifetime, so
 // mbarrier parities keep alternating):
@@ -57,35 +62,35 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 // unit.  2 gains ~3 % in a short burst at full clock, but the extra instructions cost ~1.5 % once the
 // 1 kW power cap holds the clock down, which is where a sustained run lives: off by default.
 constexpr int kPolyOf8 = MINFER_ATTN_POLY_OF_8;
-#ifndef MINFER_ATTN_P_CHUNKS
-#define MINFER_ATTN_P_CHUNKS 2
+#ifndef MINFER_ATTN_P_SPLIT
+#define MINFER_ATTN_P_SPLIT 2
 #endif
-// P is published to the MMA warp in this many pieces per key tile (1, 2 or 4): with more than one, the PV
-// MMAs of the early pieces run under the rest of the exponentials, and only the last piece's MMAs and the
-// next S stay on the slot's critical path.
-constexpr int kPChunks = MINFER_ATTN_P_CHUNKS;
-static_assert(kPChunks == 1 || kPChunks == 2 || kPChunks == 4, "P is written as four 32-key pieces");
+// P is written as four 32-key chunks and published to the MMA warp in two pieces: chunks [0, kPSplit)
+// and [kPSplit, 4).  The PV MMAs of the first piece run under the second piece's exponentials, so only
+// the second piece's MMAs and the next S stay on the slot's critical path.  0 publishes P in one piece.
+constexpr int kPSplit = MINFER_ATTN_P_SPLIT;
+static_assert(kPSplit >= 0 && kPSplit <= 3, "P is written as four 32-key chunks");
+constexpr int kPPieces = kPSplit == 0 ? 1 : 2;
 
 // barrier indices ([2] = one per slot)
 constexpr int kQFull = 0;
 constexpr int kQEmpty = 2;
 constexpr int kSFull = 4;
-constexpr int kPFull = 16;   // [2 slots][4 pieces]: one barrier per piece, so a fast thread's next piece cannot complete a phase early
+constexpr int kPFull = 16;   // [2 slots][4]: one barrier per piece (two used), so a fast thread's next piece cannot complete a phase early
 constexpr int kODone = 8;
 constexpr int kOFree = 10;
 constexpr int kSched = 12;   // [kSchedRing] item published by the TMA warp
 constexpr int kSchedRing = 4; // the TMA warp is never more than two items ahead of the slowest role
-constexpr int kKvFull = 24;  // [kStages], then kKvEmpty [kStages]
+constexpr int kSchedFree = 24;  // [kSchedRing] every consumer role has finished the item of this ring entry
+constexpr int kKvFull = 28;  // [kStages], then kKvEmpty [kStages]
+constexpr int kMaxList = 1024;  // key tiles a masked call may have (seq_k <= 131072)
 
 // Optional accounting for tuning (compiled in only with -DMINFER_ATTN_TRACE): thread 0 of every CTA
 // (slot 0, row 0) sums where its clocks went and writes 8 words behind the 16 status words.
 #ifdef MINFER_ATTN_TRACE
 #define P_ACC(stmt) do { if (acc_on) { stmt; } } while (0)
-// timeline of CTA 0's first item: role r, tile j, event e -> clock64()
-#define P_TL(r, jj, e) do { if (tl_on && k == 0 && (jj) < 64) tl_buf[((r) * 64 + (jj)) * 12 + (e)] = clock64(); } while (0)
 #else
 #define P_ACC(stmt) do { } while (0)
-#define P_TL(r, jj, e) do { } while (0)
 #endif
 
 __device__ __forceinline__ void report_p(int32_t* status, int site) {
@@ -99,7 +104,7 @@ __device__ __forceinline__ void report_p(int32_t* status, int site) {
 // One work item: the two slots' heads, first query rows and key-tile counts.
 struct Item {
   int b, kvh;
-  int head[2], q0[2], n[2];
+  int head[2], q0[2], n[2];  // n: key tiles of the slot when they are a prefix (causal / unmasked calls)
 };
 
 __device__ __forceinline__ Item decode_item(const PrefillArgs& a, int id, bool by_kv_set) {
@@ -156,7 +161,31 @@ __device__ __forceinline__ int item_id(int k, int n_items) {
   return id < n_items ? id : -1;
 }
 
-template <int D, bool BF16>
+// What a role needs to walk one item's key tiles.  Causal / unmasked calls: the tiles of slot s are the
+// prefix [0, n[s]).  Dense-mask calls (kMasked): the scheduler warp compacts the per-tile classes written
+// by mask_classify_kernel (0 = nothing visible, 1 = all visible, 2 = mixed) into a list of the key tiles
+// at least one slot must visit, published with the item through the shared-memory ring; tiles on nobody's
+// list are neither loaded nor computed, and mask bytes are read only for mixed tiles.
+// flag bits per listed tile: slot s visits it (1 << 2s), and must read mask bytes for it (2 << 2s).
+struct TileList {
+  int n_u;                 // listed tiles
+  int nvis[2];             // of which slot s visits
+  const uint16_t* tiles;   // kMasked only
+  const uint8_t* flags;    // kMasked only
+  int n0, n1;              // prefix lengths otherwise
+  template <bool kMasked>
+  __device__ __forceinline__ int tile_at(int i) const {
+    if constexpr (kMasked) return tiles[i];
+    else return i;
+  }
+  template <bool kMasked>
+  __device__ __forceinline__ uint32_t flag_at(int i) const {
+    if constexpr (kMasked) return flags[i];
+    else return (i < n0 ? 1u : 0u) | (i < n1 ? 4u : 0u);
+  }
+};
+
+template <int D, bool BF16, bool kMasked>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -166,7 +195,8 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #ifndef MINFER_ATTN_STAGES128
 #define MINFER_ATTN_STAGES128 4
 #endif
-  constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
+  // ring depth: the masked form gives one 32 KB stage to the tile lists at D = 128
+  constexpr int kStages = (D == 128) ? (kMasked ? 3 : MINFER_ATTN_STAGES128) : 8;
   constexpr int kKvEmpty = kKvFull + kStages;
   constexpr int kNumBars = kKvFull + 2 * kStages;
   constexpr uint32_t kTmemCols = 512;
@@ -182,22 +212,47 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* sched_id = reinterpret_cast<volatile int*>(tmem_slot + 4);  // [kSchedRing]
+  // ring entries of the masked form: {n_u, nvis0, nvis1, -} then tile indices and flags
+  volatile int* list_hdr = reinterpret_cast<volatile int*>(tmem_slot + 8);                    // [kSchedRing][4]
+  uint16_t* u_tile = reinterpret_cast<uint16_t*>(tmem_slot + 8 + 4 * kSchedRing);            // [kSchedRing][kMaxList]
+  uint8_t* u_flag = reinterpret_cast<uint8_t*>(u_tile + (kMasked ? kSchedRing * kMaxList : 0));  // [kSchedRing][kMaxList]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int n_items = a.items_x * a.items_y * a.batch;
   const bool dynamic = a.counter != nullptr;
-#ifdef MINFER_ATTN_TRACE
-  const bool tl_on = a.status != nullptr && blockIdx.x == 0 && (tid & 31) == 0;
-  long long* tl_buf = reinterpret_cast<long long*>(a.status + 16) + 148 * 2 * 12;
-  const int tl_role = warp == 0 ? 0 : warp == 4 ? 1 : warp == 1 ? 2 : 4;  // other softmax warps write to a dump row
-#endif
-  // k-th item of this CTA as seen by a consumer role (MMA, softmax): from the ring
-  // when items are claimed dynamically, else by the static rule; -1 = no more
+  // items (and, for dense masks, their tile lists) reach the consumer roles through the ring
+  const bool use_ring = dynamic || kMasked;
+  // k-th item of this CTA as seen by a consumer role (MMA, softmax): from the ring, else by the static
+  // rule; -1 = no more
   auto next_item = [&](int k, bool& ok) -> int {
-    if (!dynamic) return item_id(k, n_items);
+    if (!use_ring) return item_id(k, n_items);
     if (!(ok = mbar_wait(&bars[kSched + k % kSchedRing], (k / kSchedRing) & 1, abort_flag))) return -1;
     return sched_id[k % kSchedRing];
+  };
+  // a consumer role is done with the k-th item: its ring entry may be reused (count: 257 arrivals)
+  auto release_item = [&](int k) {
+    if (use_ring) mbar_arrive(&bars[kSchedFree + k % kSchedRing]);
+  };
+  auto list_of = [&](const Item& it, int k) -> TileList {
+    TileList v;
+    v.n0 = it.n[0];
+    v.n1 = it.n[1];
+    if constexpr (kMasked) {
+      const int e = k % kSchedRing;
+      v.n_u = list_hdr[e * 4 + 0];
+      v.nvis[0] = list_hdr[e * 4 + 1];
+      v.nvis[1] = list_hdr[e * 4 + 2];
+      v.tiles = u_tile + e * kMaxList;
+      v.flags = u_flag + e * kMaxList;
+    } else {
+      v.n_u = max(it.n[0], it.n[1]);
+      v.nvis[0] = it.n[0];
+      v.nvis[1] = it.n[1];
+      v.tiles = nullptr;
+      v.flags = nullptr;
+    }
+    return v;
   };
 
   if (tid == 0) {
@@ -209,7 +264,10 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_init(&bars[kODone + i], 1);
       mbar_init(&bars[kOFree + i], 128);
     }
-    for (int i = 0; i < kSchedRing; ++i) mbar_init(&bars[kSched + i], 1);
+    for (int i = 0; i < kSchedRing; ++i) {
+      mbar_init(&bars[kSched + i], 1);
+      mbar_init(&bars[kSchedFree + i], 257);  // the MMA warp's leader and the 256 softmax threads
+    }
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&bars[kKvFull + i], 1);
       mbar_init(&bars[kKvEmpty + i], 1);
@@ -230,9 +288,10 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
     if (warp == 9) {
       // ==================================================================
-      // TMA producer (converged warp, one elected lane issues)
+      // Scheduler + TMA producer (converged warp, one elected lane issues)
       // ==================================================================
       const bool leader = elect_one() != 0;
+      const int lane = tid & 31;
       if (leader) {
         tma_prefetch_desc(&tm_q);
         tma_prefetch_desc(&tm_k);
@@ -265,19 +324,72 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             id = __shfl_sync(0xFFFFFFFFu, id, leader_lane);
           }
           if (id >= n_items) id = -1;
-          if (leader) {
-            sched_id[k % kSchedRing] = id;
-            __threadfence_block();
-            mbar_arrive(&bars[kSched + k % kSchedRing]);
-          }
         } else {
           id = item_id(k, n_items);
         }
+        Item it{};
+        if (id >= 0) it = decode_item(a, id, dynamic && a.order_by_kv_set);
+        if (use_ring) {
+          const int e = k % kSchedRing;
+          // the entry's previous item (k - kSchedRing) must have been left by every consumer role
+          if (k >= kSchedRing &&
+              !(ok = mbar_wait(&bars[kSchedFree + e], ((k / kSchedRing) - 1) & 1u, abort_flag))) {
+            report_p(a.status, 22);
+            break;
+          }
+          if constexpr (kMasked) {
+            if (id >= 0) {
+              // compact the tile classes of the two slots into the entry's visit list
+              const int n_kt = (a.seq_k + kTileN - 1) / kTileN;
+              const int n_qt = (a.seq_q + kTileM - 1) / kTileM;
+              const bool act0 = it.q0[0] < a.seq_q, act1 = it.q0[1] < a.seq_q;
+              const uint8_t* c0 =
+                  (a.cls && act0) ? a.cls + (static_cast<size_t>(it.b) * n_qt + it.q0[0] / kTileM) * n_kt : nullptr;
+              const uint8_t* c1 =
+                  (a.cls && act1) ? a.cls + (static_cast<size_t>(it.b) * n_qt + it.q0[1] / kTileM) * n_kt : nullptr;
+              uint16_t* lt = u_tile + e * kMaxList;
+              uint8_t* lf = u_flag + e * kMaxList;
+              int count = 0, v0 = 0, v1 = 0;
+              for (int base = 0; base < n_kt; base += 32) {
+                const int t = base + lane;
+                uint32_t f = 0;
+                if (t < n_kt) {
+                  // without a class table every tile counts as mixed
+                  const uint32_t k0 = act0 ? (c0 ? c0[t] : 2u) : 0u;
+                  const uint32_t k1 = act1 ? (c1 ? c1[t] : 2u) : 0u;
+                  if (k0) f |= 1u | (k0 == 2u ? 2u : 0u);
+                  if (k1) f |= 4u | (k1 == 2u ? 8u : 0u);
+                }
+                const uint32_t m = __ballot_sync(0xFFFFFFFFu, f != 0);
+                if (f) {
+                  const int pos = count + __popc(m & ((1u << lane) - 1u));
+                  if (pos < kMaxList) {
+                    lt[pos] = static_cast<uint16_t>(t);
+                    lf[pos] = static_cast<uint8_t>(f);
+                  }
+                }
+                count += __popc(m);
+                v0 += __popc(__ballot_sync(0xFFFFFFFFu, (f & 1u) != 0));
+                v1 += __popc(__ballot_sync(0xFFFFFFFFu, (f & 4u) != 0));
+              }
+              if (lane == 0) {
+                list_hdr[e * 4 + 0] = min(count, kMaxList);
+                list_hdr[e * 4 + 1] = v0;
+                list_hdr[e * 4 + 2] = v1;
+              }
+              __syncwarp();
+            }
+          }
+          if (leader) sched_id[e] = id;
+          __threadfence_block();
+          __syncwarp();
+          if (leader) mbar_arrive(&bars[kSched + e]);
+        }
         if (id < 0) break;
-        const Item it = decode_item(a, id, dynamic && a.order_by_kv_set);
+        const TileList tl = list_of(it, k);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
-          if (it.n[s] == 0 || !ok) continue;
+          if (tl.nvis[s] == 0 || !ok) continue;
           if (q_loads[s] > 0 &&
               !(ok = mbar_wait(&bars[kQEmpty + s], (q_loads[s] - 1) & 1u, abort_flag))) {
             report_p(a.status, 21);
@@ -286,7 +398,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           load_tile(&tm_q, q_addr + s * kTileBytes, &bars[kQFull + s], a.q_pos, it.b, it.head[s], it.q0[s]);
           ++q_loads[s];
         }
-        const int n_loads = 2 * max(it.n[0], it.n[1]);  // K0 V0 K1 V1 ...
+        const int n_loads = 2 * tl.n_u;  // K V K V ... of the listed tiles
         for (int t = 0; t < n_loads && ok; ++t, ++r) {
           const uint32_t st = r % kStages;
           if (r >= kStages && !(ok = mbar_wait(&bars[kKvEmpty + st], ((r / kStages) - 1) & 1u, abort_flag))) {
@@ -294,7 +406,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             break;
           }
           load_tile((t & 1) ? &tm_v : &tm_k, kv_addr + st * kTileBytes, &bars[kKvFull + st], a.kv_pos, it.b, it.kvh,
-                    (t >> 1) * kTileN);
+                    tl.template tile_at<kMasked>(t >> 1) * kTileN);
         }
       }
       if (!ok || *abort_flag) {
@@ -340,97 +452,118 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         if (leader) umma_commit(&bars[kSFull + s]);
       };
-      // piece c of kPChunks of O_s (+)= P_s * V(stage st); the last piece signals o_done
+      // piece c of O_s (+)= P_s * V(stage st); the last piece signals o_done
       auto issue_pv = [&](int s, uint32_t st, int c, bool accumulate) {
-        constexpr int kSteps = kTileN / 16 / kPChunks;
+        const int kk0 = (c == 0) ? 0 : 2 * kPSplit;  // 16-key steps [kk0, kk1)
+        const int kk1 = (c == kPPieces - 1) ? kTileN / 16 : 2 * kPSplit;
         const uint32_t va = v_lo + st * (kTileBytes >> 4);
         const uint32_t tp = tmem_base + s * kTileN;  // P: packed 16-bit pairs, 8 columns per 16 keys
         const uint32_t to = tmem_base + 256 + s * 128;
 #pragma unroll
-        for (int i = 0; i < kSteps; ++i) {
-          const int kk = c * kSteps + i;
+        for (int kk = 0; kk < kTileN / 16; ++kk) {
+          if (kk < kk0 || kk >= kk1) continue;
           if (leader) {
-            if (i == 0) umma_ts(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO, accumulate ? 1u : 0u);
+            if (kk == kk0) umma_ts(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO, accumulate ? 1u : 0u);
             else umma_ts_acc(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO);
           }
         }
-        if (c == kPChunks - 1 && leader) umma_commit(&bars[kODone + s]);
+        if (c == kPPieces - 1 && leader) umma_commit(&bars[kODone + s]);
       };
 
-      uint32_t tiles[2] = {0u, 0u};  // key tiles finished per slot (parity of p_full)
-      uint32_t items[2] = {0u, 0u};  // items started per slot (parity of q_full / o_free)
+      uint32_t tiles[2] = {0u, 0u};  // key tiles finished per slot over the CTA's lifetime (parity of p_full)
+      uint32_t items[2] = {0u, 0u};  // items in which the slot had work (parity of q_full / o_free)
       uint32_t r = 0;                // K/V ring position, in step with the TMA warp
       for (int k = 0; ok; ++k) {
         const int id = next_item(k, ok);
         if (!ok) { report_p(a.status, 37); break; }
         if (id < 0) break;
         const Item it = decode_item(a, id, dynamic && a.order_by_kv_set);
-        const int n_max = max(it.n[0], it.n[1]);
-        if (n_max == 0) continue;
+        const TileList tl = list_of(it, k);
+        if (tl.n_u == 0) {
+          if (leader) release_item(k);
+          continue;
+        }
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
-          if (it.n[s] > 0 && ok && !(ok = mbar_wait(&bars[kQFull + s], items[s] & 1u, abort_flag)))
+          if (tl.nvis[s] > 0 && ok && !(ok = mbar_wait(&bars[kQFull + s], items[s] & 1u, abort_flag)))
             report_p(a.status, 30);
         }
         if (!ok) break;
-        // first K tile of the item
+        // dense masks: S / PV tiles issued per slot in this item (a prefix needs no counting)
+        [[maybe_unused]] int s_issued[2] = {0, 0};
+        [[maybe_unused]] int pv_done[2] = {0, 0};
+        // was the S just issued for listed tile `idx` the slot's last of the item?
+        auto last_s = [&](int s, int idx) -> bool {
+          if constexpr (kMasked) return ++s_issued[s] == tl.nvis[s];
+          else return idx + 1 == tl.nvis[s];
+        };
+        // first listed K tile
         if (!(ok = mbar_wait(&bars[kKvFull + r % kStages], (r / kStages) & 1u, abort_flag))) { report_p(a.status, 31); break; }
         tc_fence_after();
+        {
+          const uint32_t f0 = tl.template flag_at<kMasked>(0);
 #pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          if (it.n[s] > 0) {
-            issue_s(s, r % kStages);
-            if (it.n[s] == 1 && leader) umma_commit(&bars[kQEmpty + s]);  // that was the slot's last S of the item
+          for (int s = 0; s < 2; ++s) {
+            if (f0 & (1u << (2 * s))) {
+              issue_s(s, r % kStages);
+              if (last_s(s, 0) && leader) umma_commit(&bars[kQEmpty + s]);  // the slot's last S of the item
+            }
           }
         }
         if (leader) umma_commit(&bars[kKvEmpty + r % kStages]);
 
-        for (int j = 0; j < n_max && ok; ++j) {
-          const uint32_t rv = r + 2 * j + 1;  // ring position of V_j
-          const uint32_t rk = r + 2 * j + 2;  // ring position of K_{j+1}
+        // Per listed tile i and slot s: PV_s(i) if s visits i, then S_s(i+1) if s visits i+1.  Only K of
+        // the next listed tile is ever needed ahead, so the ring cannot deadlock however sparse a slot's
+        // visits are.
+        for (int i = 0; i < tl.n_u && ok; ++i) {
+          const uint32_t rv = r + 2 * i + 1;  // ring position of V of listed tile i
+          const uint32_t rk = r + 2 * i + 2;  // ring position of K of listed tile i+1
           const uint32_t stv = rv % kStages, stk = rk % kStages;
+          const uint32_t f = tl.template flag_at<kMasked>(i);
+          const uint32_t fn = (i + 1 < tl.n_u) ? tl.template flag_at<kMasked>(i + 1) : 0u;
           if (!(ok = mbar_wait(&bars[kKvFull + stv], (rv / kStages) & 1u, abort_flag))) { report_p(a.status, 32); break; }
           bool k_waited = false;
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
-            if (!ok || j >= it.n[s]) continue;
-            if (j == 0 && items[s] > 0) {
-              // O_s still holds the previous item's result until its epilogue has read it
-              if (!(ok = mbar_wait(&bars[kOFree + s], (items[s] - 1) & 1u, abort_flag))) { report_p(a.status, 35); continue; }
-            }
-            P_TL(3, j, s * 6 + 0);
-#pragma unroll
-            for (int c = 0; c < kPChunks; ++c) {
-              if (!ok) continue;
-              if (!(ok = mbar_wait(&bars[kPFull + 4 * s + c], tiles[s] & 1u, abort_flag))) { report_p(a.status, 33); continue; }
-              tc_fence_after();
-              P_TL(3, j, s * 6 + 1 + 2 * (c & 1));
-              issue_pv(s, stv, c, j > 0 || c > 0);
-              P_TL(3, j, s * 6 + 2 + 2 * (c & 1));
-            }
             if (!ok) continue;
-            ++tiles[s];
-            if (j + 1 < it.n[s]) {
+            if (f & (1u << (2 * s))) {
+              const bool first_pv = kMasked ? pv_done[s] == 0 : i == 0;
+              if (first_pv && items[s] > 0) {
+                // O_s still holds the previous item's result until its epilogue has read it
+                if (!(ok = mbar_wait(&bars[kOFree + s], (items[s] - 1) & 1u, abort_flag))) { report_p(a.status, 35); continue; }
+              }
+#pragma unroll
+              for (int c = 0; c < kPPieces; ++c) {
+                if (!ok) continue;
+                if (!(ok = mbar_wait(&bars[kPFull + 4 * s + c], tiles[s] & 1u, abort_flag))) { report_p(a.status, 33); continue; }
+                tc_fence_after();
+                issue_pv(s, stv, c, !first_pv || c > 0);
+              }
+              if (!ok) continue;
+              ++tiles[s];
+              if constexpr (kMasked) ++pv_done[s];
+            }
+            if (fn & (1u << (2 * s))) {
               if (!k_waited) {
                 if (!(ok = mbar_wait(&bars[kKvFull + stk], (rk / kStages) & 1u, abort_flag))) { report_p(a.status, 34); continue; }
                 k_waited = true;
                 tc_fence_after();
               }
               issue_s(s, stk);
-              P_TL(3, j, s * 6 + 5);
-              if (j + 2 == it.n[s] && leader) umma_commit(&bars[kQEmpty + s]);  // last S of the item for this slot
+              if (last_s(s, i + 1) && leader) umma_commit(&bars[kQEmpty + s]);  // last S of the item for this slot
             }
           }
           if (!ok) break;
           if (leader) {
             umma_commit(&bars[kKvEmpty + stv]);
-            if (j + 1 < n_max) umma_commit(&bars[kKvEmpty + stk]);
+            if (i + 1 < tl.n_u) umma_commit(&bars[kKvEmpty + stk]);
           }
         }
-        r += 2 * n_max;
+        r += 2 * tl.n_u;
 #pragma unroll
         for (int s = 0; s < 2; ++s)
-          if (it.n[s] > 0) ++items[s];
+          if (tl.nvis[s] > 0) ++items[s];
+        if (leader) release_item(k);
       }
       __syncwarp();
     }
@@ -441,9 +574,11 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
     const int s = warp >> 2;
     const int row = tid & 127;
+    const int lane = tid & 31;
     const uint32_t t_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tmem_s = tmem_base + s * kTileN + t_lane;
     const uint32_t tmem_o = tmem_base + 256 + s * 128 + t_lane;
+    const uint32_t visit_bit = 1u << (2 * s), mixed_bit = 2u << (2 * s);
     const float sl2 = a.scale_log2;
     const int off = a.seq_k - a.seq_q;
     bool ok = true;
@@ -460,20 +595,41 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       if (!ok) { report_p(a.status, 43); break; }
       if (id < 0) break;
       const Item it = decode_item(a, id, dynamic && a.order_by_kv_set);
-      const int nt = s ? it.n[1] : it.n[0];
-      if (nt == 0) continue;
+      const TileList tl = list_of(it, k);
       const int q0s = s ? it.q0[1] : it.q0[0];
+      const int nvis = s ? tl.nvis[1] : tl.nvis[0];
       const int heads = s ? it.head[1] : it.head[0];
       const int r_glob = q0s + row;
+      if (nvis == 0) {
+        if (kMasked && q0s < a.seq_q && r_glob < a.seq_q) {
+          // no key tile holds a visible key for this slot: the rows are zeros
+          uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) +
+                          2 * (static_cast<size_t>(it.b) * a.out_stride[0] + static_cast<size_t>(heads) * a.out_stride[1] +
+                               static_cast<size_t>(r_glob) * a.out_stride[2]);
+#pragma unroll
+          for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        release_item(k);
+        continue;
+      }
+      const uint8_t* mrow =
+          kMasked ? a.mask + (static_cast<size_t>(it.b) * a.seq_q + min(r_glob, a.seq_q - 1)) * a.seq_k : nullptr;
       float m_ref = -INFINITY;  // reference maximum the stored P and O are relative to
       float l_run = 0.f;
+      int jm = 0;  // key tiles this slot has processed in this item (dense masks; else the loop index)
 
-      for (int j = 0; j < nt; ++j, ++jt) {
-        const int kv0 = j * kTileN;
+      const int n_iter = kMasked ? tl.n_u : nvis;
+      for (int i = 0; i < n_iter; ++i) {
+        uint32_t fl = visit_bit;
+        int kv0 = i * kTileN;
+        if constexpr (kMasked) {
+          fl = tl.flags[i];
+          if (!(fl & visit_bit)) continue;
+          kv0 = tl.tiles[i] * kTileN;
+        }
+        const int j = kMasked ? jm : i;
         P_ACC(acc_c = clock64());
-        P_TL(tl_role, j, 0);
         if (!(ok = mbar_wait(&bars[kSFull + s], jt & 1u, abort_flag))) { report_p(a.status, 40); break; }
-        P_TL(tl_role, j, 1);
         P_ACC(acc_c2 = clock64(); if (j == 0) acc_first += acc_c2 - acc_c; else acc_wait += acc_c2 - acc_c);
         tc_fence_after();
 
@@ -481,16 +637,34 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
         for (int c = 0; c < kTileN / 32; ++c)
           tmem_ld32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
-        P_TL(tl_role, j, 2);
         tc_wait_ld();
-        P_TL(tl_role, j, 3);
         P_ACC(acc_c = clock64(); acc_ld += acc_c - acc_c2);
 
-        // ---- masking: only the diagonal and the ragged last tile need it ----
+        // ---- masking (tile-uniform decision): mask bytes only for mixed tiles of a dense mask; else only
+        // the diagonal and the ragged last tile need it ----
         const bool tail = kv0 + kTileN > a.seq_k;
-        const bool diag = a.causal && (kv0 + kTileN - 1 > q0s + off);
-        if (tail || diag) {
-          const int lim = a.causal ? min(a.seq_k - 1, r_glob + off) : a.seq_k - 1;
+        const bool diag = !kMasked && a.causal && (kv0 + kTileN - 1 > q0s + off);
+        if (kMasked && (fl & mixed_bit)) {
+          if (!tail && a.mask_vec) {
+            const uint4* mp = reinterpret_cast<const uint4*>(mrow + kv0);
+#pragma unroll
+            for (int c = 0; c < kTileN / 16; ++c) {
+              const uint4 mv = __ldg(mp + c);
+              const uint32_t w[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+              for (int e = 0; e < 16; ++e)
+                if (((w[e >> 2] >> ((e & 3) * 8)) & 0xFFu) == 0) sr[c * 16 + e] = 0xFF800000u;
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < kTileN; ++c) {
+              const int col = kv0 + c;
+              const bool vis = col < a.seq_k && mrow[col] != 0;
+              if (!vis) sr[c] = 0xFF800000u;
+            }
+          }
+        } else if (tail || diag) {
+          const int lim = (!kMasked && a.causal) ? min(a.seq_k - 1, r_glob + off) : a.seq_k - 1;
 #pragma unroll
           for (int c = 0; c < kTileN; ++c)
             if (kv0 + c > lim) sr[c] = 0xFF800000u;
@@ -528,7 +702,6 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           }
         }
 
-        P_TL(tl_role, j, 4);
         P_ACC(acc_c2 = clock64(); acc_max += acc_c2 - acc_c);
         // ---- P = exp2(S*c - m*c) -> 16-bit pairs -> tensor memory (over S) ----
         const float mb = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
@@ -544,7 +717,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             const float2 x = __ffma2_rn(sp, sl2_2, nmb_2);
             float2 p;
             // kPolyOf8 of every 8 pairs go through the FMA-pipe polynomial, the rest
-            // through the special-function unit, so both units stay busy
+            // through the special-function unit
             if ((e & 7) < kPolyOf8) {
               p = ex2_poly2(x);
             } else {
@@ -555,16 +728,16 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             pk[e] = pack2<BF16>(p.x, p.y);
           }
           tmem_st16(tmem_s + c * 16, pk);
-          P_TL(tl_role, j, 5 + c);
-          if ((c + 1) % (4 / kPChunks) == 0) {
+          if (c == 3 || c + 1 == kPSplit) {
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(&bars[kPFull + 4 * s + (c + 1) * kPChunks / 4 - 1]);
-            P_TL(tl_role, j, c == 3 ? 10 : 9);
+            mbar_arrive(&bars[kPFull + 4 * s + (c == 3 ? kPPieces - 1 : 0)]);
           }
         }
         l_run += sum2.x + sum2.y;
         P_ACC(acc_exp += clock64() - acc_c2);
+        if constexpr (kMasked) ++jm;
+        ++jt;
       }
       if (!ok) break;
 
@@ -580,7 +753,6 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       // a 128-byte-swizzled tensor map) and one lane hands the box to the TMA unit; rows past seq_q are
       // clipped by the tensor map.
       {
-        const int lane = tid & 31;
         const uint32_t stage = smem_u32(s_epi + warp * kEpiBytes);
         const int row0 = q0s + (warp & 3) * 32;  // first row of this warp
         auto pick = [&](int i) { return a.out_pos[0] == i ? it.b : (a.out_pos[1] == i ? heads : row0); };
@@ -616,8 +788,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
       }
       P_ACC(acc_epi += clock64() - acc_c);
+      release_item(k);
     }
-    if ((tid & 31) == 0) bulk_wait_all();  // the staging buffers stay allocated until the last box has left
+    if (lane == 0) bulk_wait_all();  // the staging buffers stay allocated until the last box has left
 #ifdef MINFER_ATTN_TRACE
     if (acc_on) {
       long long* w = reinterpret_cast<long long*>(a.status + 16) + (blockIdx.x * 2 + s) * 12;
@@ -635,12 +808,14 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   }
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool kMasked>
 cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                                const CUtensorMap& to, PrefillArgs a,
                                cudaStream_t stream) {
-  constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
-  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 8 * kEpiBytes + 512 + 1024;
+  constexpr int kStages = (D == 128) ? (kMasked ? 3 : MINFER_ATTN_STAGES128) : 8;
+  // tiles, epilogue staging, barriers and ring heads, (dense masks) the ring's tile lists, alignment slack
+  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 8 * kEpiBytes + 768 +
+                          (kMasked ? kSchedRing * kMaxList * 3 : 0) + 1024;
   static bool attr_done[64] = {};
   static int sm_count[64] = {};
   int dev = 0;
@@ -648,7 +823,7 @@ cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, con
   if (e != cudaSuccess) return e;
   if (dev >= 64) return cudaErrorInvalidDevice;
   if (!attr_done[dev]) {
-    e = cudaFuncSetAttribute(prefill_persist_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(prefill_persist_kernel<D, BF16, kMasked>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
@@ -670,7 +845,7 @@ cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, con
     e = cudaMemsetAsync(a.counter, 0, sizeof(int), stream);
     if (e != cudaSuccess) return e;
   }
-  prefill_persist_kernel<D, BF16><<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, a);
+  prefill_persist_kernel<D, BF16, kMasked><<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, a);
   return cudaGetLastError();
 }
 
@@ -678,9 +853,18 @@ cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, con
 
 cudaError_t launch_prefill_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                                    const CUtensorMap& to, const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream) {
+  if (a.mask != nullptr) {
+    if (head_dim == 128)
+      return bf16 ? launch_persist_one<128, true, true>(tq, tk, tv, to, a, stream)
+                  : launch_persist_one<128, false, true>(tq, tk, tv, to, a, stream);
+    return bf16 ? launch_persist_one<64, true, true>(tq, tk, tv, to, a, stream)
+                : launch_persist_one<64, false, true>(tq, tk, tv, to, a, stream);
+  }
   if (head_dim == 128)
-    return bf16 ? launch_persist_one<128, true>(tq, tk, tv, to, a, stream) : launch_persist_one<128, false>(tq, tk, tv, to, a, stream);
-  return bf16 ? launch_persist_one<64, true>(tq, tk, tv, to, a, stream) : launch_persist_one<64, false>(tq, tk, tv, to, a, stream);
+    return bf16 ? launch_persist_one<128, true, false>(tq, tk, tv, to, a, stream)
+                : launch_persist_one<128, false, false>(tq, tk, tv, to, a, stream);
+  return bf16 ? launch_persist_one<64, true, false>(tq, tk, tv, to, a, stream)
+              : launch_persist_one<64, false, false>(tq, tk, tv, to, a, stream);
 }
 
 }  // namespace minfer_attn

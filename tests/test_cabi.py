@@ -78,8 +78,8 @@ def test_workspace_size_formula():
 def test_prefill_mask_workspace_size():
     from minfer.kernels.torch_ext import _lib
     L = _lib.lib
-    assert L.minfer_attn_prefill_workspace_bytes(4, 4096, 4096) == 4 * 32 * 32
-    assert L.minfer_attn_prefill_workspace_bytes(1, 129, 1) == 16   # never below the 16 bytes of the work-item counter
+    assert L.minfer_attn_prefill_workspace_bytes(4, 4096, 4096) == 16 + 4 * 32 * 32   # work-item counter + tile classes
+    assert L.minfer_attn_prefill_workspace_bytes(1, 129, 1) == 16 + 2
     assert L.minfer_attn_prefill_workspace_bytes(0, 128, 128) == 0
     p = _lib.PrefillParams()
     p.q = p.k = p.v = p.out = p.mask = 0x1000

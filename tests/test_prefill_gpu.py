@@ -110,7 +110,7 @@ def test_dense_mask_without_workspace_matches(kerns):
         p.dtype, p.causal, p.softmax_scale, p.flags = _lib.F16, 0, 0.0, 0
         if use_ws:
             need = _lib.lib.minfer_attn_prefill_workspace_bytes(B, L, L)
-            assert need == 16  # 4 x 4 tile classes
+            assert need == 16 + 16  # work-item counter + 4 x 4 tile classes
             ws = torch.empty(need, dtype=torch.uint8, device="cuda")
             p.workspace, p.workspace_bytes = ws.data_ptr(), need
         rc = _lib.lib.minfer_attn_prefill(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
