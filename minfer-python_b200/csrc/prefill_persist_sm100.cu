@@ -32,13 +32,19 @@
 //   o_free[s]   softmax -> MMA  the epilogue has copied O_s out of tensor memory
 // The K/V ring simply continues across items.
 //
-// Two more differences from the one-item kernel.  P is handed to the MMA warp in
-// pieces (p_full[s][piece], one barrier per piece), so the PV MMAs of the first
-// half of a key tile run while the second half's exponentials are still being
-// computed, and only the last piece's MMAs and the next S stay on the slot's
-// critical path.  And the output leaves through the TMA unit: each softmax warp
-// packs its 32 rows, 64 columns at a time, into 4 KB of swizzled shared memory and
-// one lane issues a tensor store, instead of every thread storing its own row.
+// Three more differences from the one-item kernel.  (1) One S region for both slots
+// (tensor memory: S [0,128), P0 [128,192), P1 [192,256), O0, O1): warp 8 issues every
+// score MMA, the two slots taking the region in turn, and the next one is issued as
+// soon as the softmax warps of the previous one hold their scores in registers
+// (s_free) - i.e. while that softmax runs; P has its own columns (p_free tells the
+// softmax when the PV MMAs have read them) and warp 10 issues every PV MMA.  No MMA
+// is left on a slot's critical path; what bounds the kernel is the softmax itself
+// (special-function unit + issue slots of the two warps per SM sub-partition).
+// (2) P is handed to the PV issuer in two pieces (p_full[s][piece], one barrier per
+// piece), so the PV MMAs of a tile's first half run under the second half's
+// exponentials.  (3) The output leaves through the TMA unit: each softmax warp packs
+// its 32 rows, 64 columns at a time, into 4 KB of swizzled shared memory and one lane
+// issues a tensor store, instead of every thread storing its own row.
 #include "attn_internal.h"
 #include "ptx.cuh"
 
@@ -69,6 +75,15 @@ constexpr int kPolyOf8 = MINFER_ATTN_POLY_OF_8;
 // and [kPSplit, 4).  The PV MMAs of the first piece run under the second piece's exponentials, so only
 // the second piece's MMAs and the next S stay on the slot's critical path.  0 publishes P in one piece.
 constexpr int kPSplit = MINFER_ATTN_P_SPLIT;
+#ifndef MINFER_ATTN_SHARED_S
+#define MINFER_ATTN_SHARED_S 1
+#endif
+// Tensor-memory plan.  Shared-S form: S [0,128) used by the two slots in turn, P0 [128,192), P1 [192,256),
+// O0 [256,384), O1 [384,512); the next score tile is computed while the current softmax runs.  Otherwise
+// S0 [0,128) S1 [128,256) with P written over the first 64 columns of its own S region, O as above.
+// (Dense masks at D = 128 keep the second plan: their tile lists leave room for three K/V stages only, too
+// shallow a ring once the score MMAs run a tile ahead.)
+constexpr bool kSharedSDefault = MINFER_ATTN_SHARED_S != 0;
 static_assert(kPSplit >= 0 && kPSplit <= 3, "P is written as four 32-key chunks");
 constexpr int kPPieces = kPSplit == 0 ? 1 : 2;
 
@@ -82,15 +97,20 @@ constexpr int kOFree = 10;
 constexpr int kSched = 12;   // [kSchedRing] item published by the TMA warp
 constexpr int kSchedRing = 4; // the TMA warp is never more than two items ahead of the slowest role
 constexpr int kSchedFree = 24;  // [kSchedRing] every consumer role has finished the item of this ring entry
-constexpr int kKvFull = 28;  // [kStages], then kKvEmpty [kStages]
+constexpr int kSFree = 6;       // shared-S form: the scores issued last are in registers, the S columns may be overwritten
+constexpr int kPFree = 28;      // [2] shared-S form: the PV MMAs reading the slot's P columns have finished
+constexpr int kKvFull = 30;  // [kStages], then kKvEmpty [kStages]
 constexpr int kMaxList = 1024;  // key tiles a masked call may have (seq_k <= 131072)
 
 // Optional accounting for tuning (compiled in only with -DMINFER_ATTN_TRACE): thread 0 of every CTA
 // (slot 0, row 0) sums where its clocks went and writes 8 words behind the 16 status words.
 #ifdef MINFER_ATTN_TRACE
 #define P_ACC(stmt) do { if (acc_on) { stmt; } } while (0)
+// timeline of CTA 0's first item: role r (0/1 softmax slot, 2 S issuer, 3 PV issuer), tile jj, event e
+#define P_TL(r, jj, e) do { if (tl_on && k == 0 && (jj) < 64) tl_buf[((r) * 64 + (jj)) * 12 + (e)] = clock64(); } while (0)
 #else
 #define P_ACC(stmt) do { } while (0)
+#define P_TL(r, jj, e) do { } while (0)
 #endif
 
 __device__ __forceinline__ void report_p(int32_t* status, int site) {
@@ -197,6 +217,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #endif
   // ring depth: the masked form gives one 32 KB stage to the tile lists at D = 128
   constexpr int kStages = (D == 128) ? (kMasked ? 3 : MINFER_ATTN_STAGES128) : 8;
+  constexpr bool kSharedS = kSharedSDefault && !(kMasked && D == 128);
   constexpr int kKvEmpty = kKvFull + kStages;
   constexpr int kNumBars = kKvFull + 2 * kStages;
   constexpr uint32_t kTmemCols = 512;
@@ -223,6 +244,11 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const bool dynamic = a.counter != nullptr;
   // items (and, for dense masks, their tile lists) reach the consumer roles through the ring
   const bool use_ring = dynamic || kMasked;
+#ifdef MINFER_ATTN_TRACE
+  const bool tl_on = a.status != nullptr && blockIdx.x == 0 && (tid & 127) == 0;  // threads 0, 128, 256 (S issuer); PV issuer: 320
+  const bool tl_on2 = a.status != nullptr && blockIdx.x == 0 && tid == 320;
+  long long* tl_buf = reinterpret_cast<long long*>(a.status + 16) + 148 * 2 * 12;
+#endif
   // k-th item of this CTA as seen by a consumer role (MMA, softmax): from the ring, else by the static
   // rule; -1 = no more
   auto next_item = [&](int k, bool& ok) -> int {
@@ -230,7 +256,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     if (!(ok = mbar_wait(&bars[kSched + k % kSchedRing], (k / kSchedRing) & 1, abort_flag))) return -1;
     return sched_id[k % kSchedRing];
   };
-  // a consumer role is done with the k-th item: its ring entry may be reused (count: 257 arrivals)
+  // a consumer role is done with the k-th item: its ring entry may be reused
   auto release_item = [&](int k) {
     if (use_ring) mbar_arrive(&bars[kSchedFree + k % kSchedRing]);
   };
@@ -263,10 +289,12 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       for (int c = 0; c < 4; ++c) mbar_init(&bars[kPFull + 4 * i + c], 128);
       mbar_init(&bars[kODone + i], 1);
       mbar_init(&bars[kOFree + i], 128);
+      mbar_init(&bars[kPFree + i], 1);
     }
+    mbar_init(&bars[kSFree], 128);
     for (int i = 0; i < kSchedRing; ++i) {
       mbar_init(&bars[kSched + i], 1);
-      mbar_init(&bars[kSchedFree + i], 257);  // the MMA warp's leader and the 256 softmax threads
+      mbar_init(&bars[kSchedFree + i], kSharedS ? 258 : 257);  // the MMA warps' leaders and the 256 softmax threads
     }
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&bars[kKvFull + i], 1);
@@ -423,7 +451,164 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
       }
       __syncwarp();
-    } else if (warp == 8) {
+    } else if (kSharedS && (warp == 8 || warp == 10)) {
+      // ==================================================================
+      // MMA issuers of the shared-S form (converged warps, one elected lane issues):
+      // warp 8 issues every score MMA, warp 10 every PV MMA.  The single S region is used by
+      // the two slots in turn: the next S (whichever slot's) is issued as soon as the softmax
+      // warps of the previous one hold their scores in registers (s_free), i.e. WHILE that
+      // softmax runs, and P has its own columns, so no MMA is left on a slot's critical path.
+      // ==================================================================
+      const bool leader = elect_one() != 0;
+      bool ok = true;
+      constexpr uint32_t kHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+      constexpr uint32_t kLoK = (16u >> 4) << 16;
+      constexpr uint32_t kLoV = (static_cast<uint32_t>(kBlockBytes) >> 4) << 16;  // LBO = one block for MN-major V
+      const uint32_t q_lo = (smem_u32(s_q) >> 4) | kLoK;
+      const uint32_t k_lo = (smem_u32(s_kv) >> 4) | kLoK;
+      const uint32_t v_lo = (smem_u32(s_kv) >> 4) | kLoV;
+      auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+      uint32_t items[2] = {0u, 0u};  // items in which the slot had work (parity of q_full / o_free)
+      uint32_t r = 0;                // K/V ring position, in step with the TMA warp
+
+      if (warp == 8) {
+        // ---- scores: S = Q_s K^T into the shared S columns ----
+        auto issue_s = [&](int s, uint32_t st) {
+          const uint32_t qa = q_lo + s * (kTileBytes >> 4);
+          const uint32_t ka = k_lo + st * (kTileBytes >> 4);
+#pragma unroll
+          for (int i = 0; i < kDB * 4; ++i) {
+            const uint32_t o = (i >> 2) * (kBlockBytes >> 4) + (i & 3) * 2;  // 32 bytes per 16-element k step
+            if (leader) {
+              if (i == 0) umma_ss_first(tmem_base, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
+              else umma_ss_acc(tmem_base, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
+            }
+          }
+          if (leader) umma_commit(&bars[kSFull + s]);
+        };
+        uint32_t s_count = 0;  // score tiles issued over the CTA's lifetime (parity of s_free)
+        for (int k = 0; ok; ++k) {
+          const int id = next_item(k, ok);
+          if (!ok) { report_p(a.status, 37); break; }
+          if (id < 0) break;
+          const Item it = decode_item(a, id, dynamic && a.order_by_kv_set);
+          const TileList tl = list_of(it, k);
+          if (tl.n_u == 0) {
+            if (leader) release_item(k);
+            continue;
+          }
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            if (tl.nvis[s] > 0 && ok && !(ok = mbar_wait(&bars[kQFull + s], items[s] & 1u, abort_flag)))
+              report_p(a.status, 30);
+          }
+          if (!ok) break;
+          [[maybe_unused]] int s_issued[2] = {0, 0};
+          for (int i = 0; i < tl.n_u && ok; ++i) {
+            const uint32_t rk = r + 2 * i;  // ring position of K of listed tile i
+            const uint32_t stk = rk % kStages;
+            const uint32_t f = tl.template flag_at<kMasked>(i);
+            if (!(ok = mbar_wait(&bars[kKvFull + stk], (rk / kStages) & 1u, abort_flag))) { report_p(a.status, 31); break; }
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+              if (!ok || !(f & (1u << (2 * s)))) continue;
+              // the scores issued last (either slot's) must have been copied out of the S columns
+              P_TL(2, i, s * 3 + 0);
+              if (s_count > 0 && !(ok = mbar_wait(&bars[kSFree], (s_count - 1) & 1u, abort_flag))) { report_p(a.status, 38); continue; }
+              tc_fence_after();
+              P_TL(2, i, s * 3 + 1);
+              issue_s(s, stk);
+              P_TL(2, i, s * 3 + 2);
+              ++s_count;
+              bool last;
+              if constexpr (kMasked) last = ++s_issued[s] == tl.nvis[s];
+              else last = i + 1 == tl.nvis[s];
+              if (last && leader) umma_commit(&bars[kQEmpty + s]);  // the slot's last S of the item
+            }
+            if (!ok) break;
+            if (leader) umma_commit(&bars[kKvEmpty + stk]);
+          }
+          r += 2 * tl.n_u;
+#pragma unroll
+          for (int s = 0; s < 2; ++s)
+            if (tl.nvis[s] > 0) ++items[s];
+          if (leader) release_item(k);
+        }
+      } else {
+        // ---- O_s (+)= P_s V, P from its own tensor-memory columns ----
+        auto issue_pv = [&](int s, uint32_t st, int c, bool accumulate) {
+          const int kk0 = (c == 0) ? 0 : 2 * kPSplit;  // 16-key steps [kk0, kk1)
+          const int kk1 = (c == kPPieces - 1) ? kTileN / 16 : 2 * kPSplit;
+          const uint32_t va = v_lo + st * (kTileBytes >> 4);
+          const uint32_t tp = tmem_base + 128 + s * 64;  // P: packed 16-bit pairs, 8 columns per 16 keys
+          const uint32_t to = tmem_base + 256 + s * 128;
+#pragma unroll
+          for (int kk = 0; kk < kTileN / 16; ++kk) {
+            if (kk < kk0 || kk >= kk1) continue;
+            if (leader) {
+              if (kk == kk0) umma_ts(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO, accumulate ? 1u : 0u);
+              else umma_ts_acc(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO);
+            }
+          }
+          if (c == kPPieces - 1 && leader) {
+            umma_commit(&bars[kODone + s]);
+            umma_commit(&bars[kPFree + s]);
+          }
+        };
+        uint32_t tiles[2] = {0u, 0u};  // key tiles finished per slot over the CTA's lifetime (parity of p_full)
+        for (int k = 0; ok; ++k) {
+          const int id = next_item(k, ok);
+          if (!ok) { report_p(a.status, 37); break; }
+          if (id < 0) break;
+          const Item it = decode_item(a, id, dynamic && a.order_by_kv_set);
+          const TileList tl = list_of(it, k);
+          if (tl.n_u == 0) {
+            if (leader) release_item(k);
+            continue;
+          }
+          [[maybe_unused]] int pv_done[2] = {0, 0};
+          for (int i = 0; i < tl.n_u && ok; ++i) {
+            const uint32_t rv = r + 2 * i + 1;  // ring position of V of listed tile i
+            const uint32_t stv = rv % kStages;
+            const uint32_t f = tl.template flag_at<kMasked>(i);
+            if (!(ok = mbar_wait(&bars[kKvFull + stv], (rv / kStages) & 1u, abort_flag))) { report_p(a.status, 32); break; }
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+              if (!ok || !(f & (1u << (2 * s)))) continue;
+              const bool first_pv = kMasked ? pv_done[s] == 0 : i == 0;
+              if (first_pv && items[s] > 0) {
+                // O_s still holds the previous item's result until its epilogue has read it
+                if (!(ok = mbar_wait(&bars[kOFree + s], (items[s] - 1) & 1u, abort_flag))) { report_p(a.status, 35); continue; }
+              }
+#pragma unroll
+              for (int c = 0; c < kPPieces; ++c) {
+                if (!ok) continue;
+                if (!(ok = mbar_wait(&bars[kPFull + 4 * s + c], tiles[s] & 1u, abort_flag))) { report_p(a.status, 33); continue; }
+                tc_fence_after();
+#ifdef MINFER_ATTN_TRACE
+                if (tl_on2 && k == 0 && i < 64) tl_buf[(3 * 64 + i) * 12 + s * 4 + 2 * c] = clock64();
+#endif
+                issue_pv(s, stv, c, !first_pv || c > 0);
+#ifdef MINFER_ATTN_TRACE
+                if (tl_on2 && k == 0 && i < 64) tl_buf[(3 * 64 + i) * 12 + s * 4 + 2 * c + 1] = clock64();
+#endif
+              }
+              if (!ok) continue;
+              ++tiles[s];
+              if constexpr (kMasked) ++pv_done[s];
+            }
+            if (!ok) break;
+            if (leader) umma_commit(&bars[kKvEmpty + stv]);
+          }
+          r += 2 * tl.n_u;
+#pragma unroll
+          for (int s = 0; s < 2; ++s)
+            if (tl.nvis[s] > 0) ++items[s];
+          if (leader) release_item(k);
+        }
+      }
+      __syncwarp();
+    } else if (!kSharedS && warp == 8) {
       // ==================================================================
       // MMA issuer (converged warp, one elected lane issues; descriptors are
       // (hi, lo) pairs of which only the start address in `lo` changes)
@@ -576,7 +761,8 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int row = tid & 127;
     const int lane = tid & 31;
     const uint32_t t_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tmem_s = tmem_base + s * kTileN + t_lane;
+    const uint32_t tmem_s = tmem_base + (kSharedS ? 0 : s * kTileN) + t_lane;
+    const uint32_t tmem_p = kSharedS ? tmem_base + 128 + s * 64 + t_lane : tmem_s;  // packed P
     const uint32_t tmem_o = tmem_base + 256 + s * 128 + t_lane;
     const uint32_t visit_bit = 1u << (2 * s), mixed_bit = 2u << (2 * s);
     const float sl2 = a.scale_log2;
@@ -629,7 +815,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         const int j = kMasked ? jm : i;
         P_ACC(acc_c = clock64());
+        P_TL(s, j, 0);
         if (!(ok = mbar_wait(&bars[kSFull + s], jt & 1u, abort_flag))) { report_p(a.status, 40); break; }
+        P_TL(s, j, 1);
         P_ACC(acc_c2 = clock64(); if (j == 0) acc_first += acc_c2 - acc_c; else acc_wait += acc_c2 - acc_c);
         tc_fence_after();
 
@@ -638,6 +826,12 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int c = 0; c < kTileN / 32; ++c)
           tmem_ld32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
         tc_wait_ld();
+        if constexpr (kSharedS) {
+          // the scores are in registers: the S columns may take the next score tile (either slot's)
+          tc_fence_before();
+          mbar_arrive(&bars[kSFree]);
+        }
+        P_TL(s, j, 2);
         P_ACC(acc_c = clock64(); acc_ld += acc_c - acc_c2);
 
         // ---- masking (tile-uniform decision): mask bytes only for mixed tiles of a dense mask; else only
@@ -702,8 +896,14 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           }
         }
 
+        P_TL(s, j, 3);
         P_ACC(acc_c2 = clock64(); acc_max += acc_c2 - acc_c);
-        // ---- P = exp2(S*c - m*c) -> 16-bit pairs -> tensor memory (over S) ----
+        // ---- P = exp2(S*c - m*c) -> 16-bit pairs -> tensor memory ----
+        if constexpr (kSharedS) {
+          // the PV MMAs of this slot's previous tile must have finished reading the P columns
+          if (jt > 0 && !(ok = mbar_wait(&bars[kPFree + s], (jt - 1) & 1u, abort_flag))) { report_p(a.status, 44); break; }
+          tc_fence_after();
+        }
         const float mb = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
         const float2 sl2_2 = make_float2(sl2, sl2);
         const float2 nmb_2 = make_float2(-mb, -mb);
@@ -727,11 +927,12 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             sum2 = __fadd2_rn(sum2, p);
             pk[e] = pack2<BF16>(p.x, p.y);
           }
-          tmem_st16(tmem_s + c * 16, pk);
+          tmem_st16(tmem_p + c * 16, pk);
           if (c == 3 || c + 1 == kPSplit) {
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(&bars[kPFull + 4 * s + (c == 3 ? kPPieces - 1 : 0)]);
+            P_TL(s, j, c == 3 ? 5 : 4);
           }
         }
         l_run += sum2.x + sum2.y;
