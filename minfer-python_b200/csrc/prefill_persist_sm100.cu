@@ -56,7 +56,7 @@ constexpr int kTileM = 128;
 constexpr int kTileN = 128;
 constexpr int kBlockBytes = 128 * 128;
 constexpr int kEpiBytes = 32 * 128;  // 32 rows x 64 columns of 16-bit output per softmax warp
-constexpr int kThreads = 384;  // softmax 0 (warps 0-3), softmax 1 (4-7), MMA (8), TMA (9), 2 idle warps
+constexpr int kThreads = 384;  // softmax 0 (warps 0-3), softmax 1 (4-7), score MMAs (8), scheduler + TMA (9), PV MMAs (10), idle (11)
 // setmaxnreg split of the 384 x 168 launch allocation: 8 x 208 + 4 x 88 = 12 x 168
 constexpr int kRegsSoftmax = 208;
 constexpr int kRegsOther = 88;
@@ -65,27 +65,20 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 #define MINFER_ATTN_POLY_OF_8 0
 #endif
 // Share (of 8) of the exp2 evaluations done with a cubic on the FMA pipes instead of the special-function
-// unit.  2 gains ~3 % in a short burst at full clock, but the extra instructions cost ~1.5 % once the
-// 1 kW power cap holds the clock down, which is where a sustained run lives: off by default.
+// unit.  Measured in this kernel: 1 of 8 is neutral, 2 or more cost 5 % and up (the extra instructions
+// outweigh the relieved unit): off by default.
 constexpr int kPolyOf8 = MINFER_ATTN_POLY_OF_8;
 #ifndef MINFER_ATTN_P_SPLIT
 #define MINFER_ATTN_P_SPLIT 2
 #endif
-// P is written as four 32-key chunks and published to the MMA warp in two pieces: chunks [0, kPSplit)
-// and [kPSplit, 4).  The PV MMAs of the first piece run under the second piece's exponentials, so only
-// the second piece's MMAs and the next S stay on the slot's critical path.  0 publishes P in one piece.
+// P is written as four 32-key chunks and published to the PV issuer in two pieces: chunks [0, kPSplit)
+// and [kPSplit, 4).  The PV MMAs of the first piece run under the second piece's exponentials, which
+// shortens the waits for o_done and p_free.  0 publishes P in one piece.
 constexpr int kPSplit = MINFER_ATTN_P_SPLIT;
-#ifndef MINFER_ATTN_SHARED_S
-#define MINFER_ATTN_SHARED_S 1
-#endif
-// Tensor-memory plan.  Shared-S form: S [0,128) used by the two slots in turn, P0 [128,192), P1 [192,256),
-// O0 [256,384), O1 [384,512); the next score tile is computed while the current softmax runs.  Otherwise
-// S0 [0,128) S1 [128,256) with P written over the first 64 columns of its own S region, O as above.
-// (Dense masks at D = 128 keep the second plan: their tile lists leave room for three K/V stages only, too
-// shallow a ring once the score MMAs run a tile ahead.)
-constexpr bool kSharedSDefault = MINFER_ATTN_SHARED_S != 0;
 static_assert(kPSplit >= 0 && kPSplit <= 3, "P is written as four 32-key chunks");
 constexpr int kPPieces = kPSplit == 0 ? 1 : 2;
+// Tensor-memory plan: S [0,128) used by the two slots in turn, P0 [128,192), P1 [192,256), O0 [256,384),
+// O1 [384,512); the next score tile is computed while the current softmax runs.
 
 // barrier indices ([2] = one per slot)
 constexpr int kQFull = 0;
@@ -97,10 +90,11 @@ constexpr int kOFree = 10;
 constexpr int kSched = 12;   // [kSchedRing] item published by the TMA warp
 constexpr int kSchedRing = 4; // the TMA warp is never more than two items ahead of the slowest role
 constexpr int kSchedFree = 24;  // [kSchedRing] every consumer role has finished the item of this ring entry
-constexpr int kSFree = 6;       // shared-S form: the scores issued last are in registers, the S columns may be overwritten
-constexpr int kPFree = 28;      // [2] shared-S form: the PV MMAs reading the slot's P columns have finished
+constexpr int kSFree = 6;       // the scores issued last are in registers, the S columns may be overwritten
+constexpr int kPFree = 28;      // [2] the PV MMAs reading the slot's P columns have finished
 constexpr int kKvFull = 30;  // [kStages], then kKvEmpty [kStages]
-constexpr int kMaxList = 1024;  // key tiles a masked call may have (seq_k <= 131072)
+constexpr int kMaxTiles = 1024;  // key tiles a masked call may have (seq_k <= 131072)
+constexpr int kMaskRing = 3;     // ring entries used by dense-mask calls (their bit planes must fit beside four K/V stages)
 
 // Optional accounting for tuning (compiled in only with -DMINFER_ATTN_TRACE): thread 0 of every CTA
 // (slot 0, row 0) sums where its clocks went and writes 8 words behind the 16 status words.
@@ -182,26 +176,54 @@ __device__ __forceinline__ int item_id(int k, int n_items) {
 }
 
 // What a role needs to walk one item's key tiles.  Causal / unmasked calls: the tiles of slot s are the
-// prefix [0, n[s]).  Dense-mask calls (kMasked): the scheduler warp compacts the per-tile classes written
-// by mask_classify_kernel (0 = nothing visible, 1 = all visible, 2 = mixed) into a list of the key tiles
-// at least one slot must visit, published with the item through the shared-memory ring; tiles on nobody's
-// list are neither loaded nor computed, and mask bytes are read only for mixed tiles.
-// flag bits per listed tile: slot s visits it (1 << 2s), and must read mask bytes for it (2 << 2s).
+// prefix [0, n[s]).  Dense-mask calls (kMasked): the scheduler warp turns the per-tile classes written by
+// mask_classify_kernel (0 = nothing visible, 1 = all visible, 2 = mixed) into four bit planes over the key
+// tiles, published with the item through the shared-memory ring; a tile with no bit set is neither loaded
+// nor computed, and mask bytes are read only for mixed tiles.
+// flag bits per tile: slot s visits it (1 << 2s), and must read mask bytes for it (2 << 2s).
 struct TileList {
-  int n_u;                 // listed tiles
-  int nvis[2];             // of which slot s visits
-  const uint16_t* tiles;   // kMasked only
-  const uint8_t* flags;    // kMasked only
-  int n0, n1;              // prefix lengths otherwise
+  int n_t;                        // key tiles to scan: [0, n_t)
+  int n_u;                        // of which at least one slot visits ("listed": these take K/V ring positions)
+  int nvis[2];                    // of which slot s visits
+  const volatile uint32_t* planes;  // kMasked only: [n_t / 32][4] bit planes of the flags
+  int n0, n1;                     // prefix lengths otherwise
+  // Flags of tile t.  `pw` caches the four plane words of t's group of 32 tiles (the caller scans t upwards
+  // from 0); a group nobody visits is skipped as a whole by advancing t to its last tile.
   template <bool kMasked>
-  __device__ __forceinline__ int tile_at(int i) const {
-    if constexpr (kMasked) return tiles[i];
-    else return i;
+  __device__ __forceinline__ uint32_t flag_at(int& t, uint32_t (&pw)[4]) const {
+    if constexpr (kMasked) {
+      if ((t & 31) == 0) {
+        const volatile uint32_t* g = planes + (t >> 5) * 4;
+        pw[0] = g[0];
+        pw[1] = g[1];
+        pw[2] = g[2];
+        pw[3] = g[3];
+        if ((pw[0] | pw[2]) == 0u) {
+          t += 31;
+          return 0u;
+        }
+      }
+      const int sh = t & 31;
+      return ((pw[0] >> sh) & 1u) | (((pw[1] >> sh) & 1u) << 1) | (((pw[2] >> sh) & 1u) << 2) |
+             (((pw[3] >> sh) & 1u) << 3);
+    } else {
+      return (t < n0 ? 1u : 0u) | (t < n1 ? 4u : 0u);
+    }
   }
-  template <bool kMasked>
-  __device__ __forceinline__ uint32_t flag_at(int i) const {
-    if constexpr (kMasked) return flags[i];
-    else return (i < n0 ? 1u : 0u) | (i < n1 ? 4u : 0u);
+  // Dense masks, one slot's view: bit 0 = slot s visits tile t, bit 1 = it must read mask bytes.  `pv`, `pm`
+  // cache the slot's two plane words of t's group; a group the slot does not visit is skipped as a whole.
+  __device__ __forceinline__ uint32_t slot_flag_at(int s, int& t, uint32_t& pv, uint32_t& pm) const {
+    if ((t & 31) == 0) {
+      const volatile uint32_t* g = planes + (t >> 5) * 4 + 2 * s;
+      pv = g[0];
+      pm = g[1];
+      if (pv == 0u) {
+        t += 31;
+        return 0u;
+      }
+    }
+    const int sh = t & 31;
+    return ((pv >> sh) & 1u) | (((pm >> sh) & 1u) << 1);
   }
 };
 
@@ -215,9 +237,8 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #ifndef MINFER_ATTN_STAGES128
 #define MINFER_ATTN_STAGES128 4
 #endif
-  // ring depth: the masked form gives one 32 KB stage to the tile lists at D = 128
-  constexpr int kStages = (D == 128) ? (kMasked ? 3 : MINFER_ATTN_STAGES128) : 8;
-  constexpr bool kSharedS = kSharedSDefault && !(kMasked && D == 128);
+  constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
+  constexpr int kRing = kMasked ? kMaskRing : kSchedRing;  // ring entries in use
   constexpr int kKvEmpty = kKvFull + kStages;
   constexpr int kNumBars = kKvFull + 2 * kStages;
   constexpr uint32_t kTmemCols = 512;
@@ -233,10 +254,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* sched_id = reinterpret_cast<volatile int*>(tmem_slot + 4);  // [kSchedRing]
-  // ring entries of the masked form: {n_u, nvis0, nvis1, -} then tile indices and flags
-  volatile int* list_hdr = reinterpret_cast<volatile int*>(tmem_slot + 8);                    // [kSchedRing][4]
-  uint16_t* u_tile = reinterpret_cast<uint16_t*>(tmem_slot + 8 + 4 * kSchedRing);            // [kSchedRing][kMaxList]
-  uint8_t* u_flag = reinterpret_cast<uint8_t*>(u_tile + (kMasked ? kSchedRing * kMaxList : 0));  // [kSchedRing][kMaxList]
+  // ring entries of the masked form: {n_u, nvis0, nvis1, -} and the flags' bit planes
+  volatile int* list_hdr = reinterpret_cast<volatile int*>(tmem_slot + 8);                           // [kSchedRing][4]
+  volatile uint32_t* planes = reinterpret_cast<volatile uint32_t*>(tmem_slot + 8 + 4 * kSchedRing);  // [kMaskRing][kMaxTiles / 8]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -253,30 +273,30 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   // rule; -1 = no more
   auto next_item = [&](int k, bool& ok) -> int {
     if (!use_ring) return item_id(k, n_items);
-    if (!(ok = mbar_wait(&bars[kSched + k % kSchedRing], (k / kSchedRing) & 1, abort_flag))) return -1;
-    return sched_id[k % kSchedRing];
+    if (!(ok = mbar_wait(&bars[kSched + k % kRing], (k / kRing) & 1, abort_flag))) return -1;
+    return sched_id[k % kRing];
   };
   // a consumer role is done with the k-th item: its ring entry may be reused
   auto release_item = [&](int k) {
-    if (use_ring) mbar_arrive(&bars[kSchedFree + k % kSchedRing]);
+    if (use_ring) mbar_arrive(&bars[kSchedFree + k % kRing]);
   };
   auto list_of = [&](const Item& it, int k) -> TileList {
     TileList v;
     v.n0 = it.n[0];
     v.n1 = it.n[1];
     if constexpr (kMasked) {
-      const int e = k % kSchedRing;
+      const int e = k % kRing;
+      v.n_t = (a.seq_k + kTileN - 1) / kTileN;
       v.n_u = list_hdr[e * 4 + 0];
       v.nvis[0] = list_hdr[e * 4 + 1];
       v.nvis[1] = list_hdr[e * 4 + 2];
-      v.tiles = u_tile + e * kMaxList;
-      v.flags = u_flag + e * kMaxList;
+      v.planes = planes + e * (kMaxTiles / 8);
     } else {
       v.n_u = max(it.n[0], it.n[1]);
+      v.n_t = v.n_u;
       v.nvis[0] = it.n[0];
       v.nvis[1] = it.n[1];
-      v.tiles = nullptr;
-      v.flags = nullptr;
+      v.planes = nullptr;
     }
     return v;
   };
@@ -294,7 +314,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     mbar_init(&bars[kSFree], 128);
     for (int i = 0; i < kSchedRing; ++i) {
       mbar_init(&bars[kSched + i], 1);
-      mbar_init(&bars[kSchedFree + i], kSharedS ? 258 : 257);  // the MMA warps' leaders and the 256 softmax threads
+      mbar_init(&bars[kSchedFree + i], 258);  // the two MMA warps' leaders and the 256 softmax threads
     }
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&bars[kKvFull + i], 1);
@@ -358,16 +378,16 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         Item it{};
         if (id >= 0) it = decode_item(a, id, dynamic && a.order_by_kv_set);
         if (use_ring) {
-          const int e = k % kSchedRing;
+          const int e = k % kRing;
           // the entry's previous item (k - kSchedRing) must have been left by every consumer role
-          if (k >= kSchedRing &&
-              !(ok = mbar_wait(&bars[kSchedFree + e], ((k / kSchedRing) - 1) & 1u, abort_flag))) {
+          if (k >= kRing &&
+              !(ok = mbar_wait(&bars[kSchedFree + e], ((k / kRing) - 1) & 1u, abort_flag))) {
             report_p(a.status, 22);
             break;
           }
           if constexpr (kMasked) {
             if (id >= 0) {
-              // compact the tile classes of the two slots into the entry's visit list
+              // the tile classes of the two slots -> the entry's four bit planes
               const int n_kt = (a.seq_k + kTileN - 1) / kTileN;
               const int n_qt = (a.seq_q + kTileM - 1) / kTileM;
               const bool act0 = it.q0[0] < a.seq_q, act1 = it.q0[1] < a.seq_q;
@@ -375,8 +395,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                   (a.cls && act0) ? a.cls + (static_cast<size_t>(it.b) * n_qt + it.q0[0] / kTileM) * n_kt : nullptr;
               const uint8_t* c1 =
                   (a.cls && act1) ? a.cls + (static_cast<size_t>(it.b) * n_qt + it.q0[1] / kTileM) * n_kt : nullptr;
-              uint16_t* lt = u_tile + e * kMaxList;
-              uint8_t* lf = u_flag + e * kMaxList;
+              volatile uint32_t* pl = planes + e * (kMaxTiles / 8);
               int count = 0, v0 = 0, v1 = 0;
               for (int base = 0; base < n_kt; base += 32) {
                 const int t = base + lane;
@@ -388,20 +407,20 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                   if (k0) f |= 1u | (k0 == 2u ? 2u : 0u);
                   if (k1) f |= 4u | (k1 == 2u ? 8u : 0u);
                 }
-                const uint32_t m = __ballot_sync(0xFFFFFFFFu, f != 0);
-                if (f) {
-                  const int pos = count + __popc(m & ((1u << lane) - 1u));
-                  if (pos < kMaxList) {
-                    lt[pos] = static_cast<uint16_t>(t);
-                    lf[pos] = static_cast<uint8_t>(f);
-                  }
+                const uint32_t b0 = __ballot_sync(0xFFFFFFFFu, (f & 1u) != 0), b1 = __ballot_sync(0xFFFFFFFFu, (f & 2u) != 0);
+                const uint32_t b2 = __ballot_sync(0xFFFFFFFFu, (f & 4u) != 0), b3 = __ballot_sync(0xFFFFFFFFu, (f & 8u) != 0);
+                if (lane == 0) {
+                  pl[(base >> 5) * 4 + 0] = b0;
+                  pl[(base >> 5) * 4 + 1] = b1;
+                  pl[(base >> 5) * 4 + 2] = b2;
+                  pl[(base >> 5) * 4 + 3] = b3;
                 }
-                count += __popc(m);
-                v0 += __popc(__ballot_sync(0xFFFFFFFFu, (f & 1u) != 0));
-                v1 += __popc(__ballot_sync(0xFFFFFFFFu, (f & 4u) != 0));
+                count += __popc(b0 | b2);
+                v0 += __popc(b0);
+                v1 += __popc(b2);
               }
               if (lane == 0) {
-                list_hdr[e * 4 + 0] = min(count, kMaxList);
+                list_hdr[e * 4 + 0] = count;
                 list_hdr[e * 4 + 1] = v0;
                 list_hdr[e * 4 + 2] = v1;
               }
@@ -426,15 +445,20 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           load_tile(&tm_q, q_addr + s * kTileBytes, &bars[kQFull + s], a.q_pos, it.b, it.head[s], it.q0[s]);
           ++q_loads[s];
         }
-        const int n_loads = 2 * tl.n_u;  // K V K V ... of the listed tiles
-        for (int t = 0; t < n_loads && ok; ++t, ++r) {
-          const uint32_t st = r % kStages;
-          if (r >= kStages && !(ok = mbar_wait(&bars[kKvEmpty + st], ((r / kStages) - 1) & 1u, abort_flag))) {
-            report_p(a.status, 20);
-            break;
+        // K V K V ... of the listed tiles
+        uint32_t pw[4] = {0u, 0u, 0u, 0u};
+        for (int t = 0; t < tl.n_t && ok; ++t) {
+          if (tl.template flag_at<kMasked>(t, pw) == 0u) continue;
+#pragma unroll
+          for (int h = 0; h < 2 && ok; ++h, ++r) {
+            const uint32_t st = r % kStages;
+            if (r >= kStages && !(ok = mbar_wait(&bars[kKvEmpty + st], ((r / kStages) - 1) & 1u, abort_flag))) {
+              report_p(a.status, 20);
+              break;
+            }
+            load_tile(h ? &tm_v : &tm_k, kv_addr + st * kTileBytes, &bars[kKvFull + st], a.kv_pos, it.b, it.kvh,
+                      t * kTileN);
           }
-          load_tile((t & 1) ? &tm_v : &tm_k, kv_addr + st * kTileBytes, &bars[kKvFull + st], a.kv_pos, it.b, it.kvh,
-                    tl.template tile_at<kMasked>(t >> 1) * kTileN);
         }
       }
       if (!ok || *abort_flag) {
@@ -451,9 +475,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
       }
       __syncwarp();
-    } else if (kSharedS && (warp == 8 || warp == 10)) {
+    } else if (warp == 8 || warp == 10) {
       // ==================================================================
-      // MMA issuers of the shared-S form (converged warps, one elected lane issues):
+      // MMA issuers (converged warps, one elected lane issues):
       // warp 8 issues every score MMA, warp 10 every PV MMA.  The single S region is used by
       // the two slots in turn: the next S (whichever slot's) is issued as soon as the softmax
       // warps of the previous one hold their scores in registers (s_free), i.e. WHILE that
@@ -504,25 +528,28 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           }
           if (!ok) break;
           [[maybe_unused]] int s_issued[2] = {0, 0};
-          for (int i = 0; i < tl.n_u && ok; ++i) {
-            const uint32_t rk = r + 2 * i;  // ring position of K of listed tile i
+          uint32_t pw[4] = {0u, 0u, 0u, 0u};
+          for (int t = 0, li = 0; t < tl.n_t && ok; ++t) {
+            const uint32_t f = tl.template flag_at<kMasked>(t, pw);
+            if (f == 0u) continue;
+            const uint32_t rk = r + 2 * li;  // ring position of K of this (the li-th listed) tile
             const uint32_t stk = rk % kStages;
-            const uint32_t f = tl.template flag_at<kMasked>(i);
+            ++li;
             if (!(ok = mbar_wait(&bars[kKvFull + stk], (rk / kStages) & 1u, abort_flag))) { report_p(a.status, 31); break; }
 #pragma unroll
             for (int s = 0; s < 2; ++s) {
               if (!ok || !(f & (1u << (2 * s)))) continue;
               // the scores issued last (either slot's) must have been copied out of the S columns
-              P_TL(2, i, s * 3 + 0);
+              P_TL(2, t, s * 3 + 0);
               if (s_count > 0 && !(ok = mbar_wait(&bars[kSFree], (s_count - 1) & 1u, abort_flag))) { report_p(a.status, 38); continue; }
               tc_fence_after();
-              P_TL(2, i, s * 3 + 1);
+              P_TL(2, t, s * 3 + 1);
               issue_s(s, stk);
-              P_TL(2, i, s * 3 + 2);
+              P_TL(2, t, s * 3 + 2);
               ++s_count;
               bool last;
               if constexpr (kMasked) last = ++s_issued[s] == tl.nvis[s];
-              else last = i + 1 == tl.nvis[s];
+              else last = t + 1 == tl.nvis[s];
               if (last && leader) umma_commit(&bars[kQEmpty + s]);  // the slot's last S of the item
             }
             if (!ok) break;
@@ -567,15 +594,18 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             continue;
           }
           [[maybe_unused]] int pv_done[2] = {0, 0};
-          for (int i = 0; i < tl.n_u && ok; ++i) {
-            const uint32_t rv = r + 2 * i + 1;  // ring position of V of listed tile i
+          uint32_t pw[4] = {0u, 0u, 0u, 0u};
+          for (int t = 0, li = 0; t < tl.n_t && ok; ++t) {
+            const uint32_t f = tl.template flag_at<kMasked>(t, pw);
+            if (f == 0u) continue;
+            const uint32_t rv = r + 2 * li + 1;  // ring position of V of this (the li-th listed) tile
             const uint32_t stv = rv % kStages;
-            const uint32_t f = tl.template flag_at<kMasked>(i);
+            ++li;
             if (!(ok = mbar_wait(&bars[kKvFull + stv], (rv / kStages) & 1u, abort_flag))) { report_p(a.status, 32); break; }
 #pragma unroll
             for (int s = 0; s < 2; ++s) {
               if (!ok || !(f & (1u << (2 * s)))) continue;
-              const bool first_pv = kMasked ? pv_done[s] == 0 : i == 0;
+              const bool first_pv = kMasked ? pv_done[s] == 0 : t == 0;
               if (first_pv && items[s] > 0) {
                 // O_s still holds the previous item's result until its epilogue has read it
                 if (!(ok = mbar_wait(&bars[kOFree + s], (items[s] - 1) & 1u, abort_flag))) { report_p(a.status, 35); continue; }
@@ -586,11 +616,11 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 if (!(ok = mbar_wait(&bars[kPFull + 4 * s + c], tiles[s] & 1u, abort_flag))) { report_p(a.status, 33); continue; }
                 tc_fence_after();
 #ifdef MINFER_ATTN_TRACE
-                if (tl_on2 && k == 0 && i < 64) tl_buf[(3 * 64 + i) * 12 + s * 4 + 2 * c] = clock64();
+                if (tl_on2 && k == 0 && t < 64) tl_buf[(3 * 64 + t) * 12 + s * 4 + 2 * c] = clock64();
 #endif
                 issue_pv(s, stv, c, !first_pv || c > 0);
 #ifdef MINFER_ATTN_TRACE
-                if (tl_on2 && k == 0 && i < 64) tl_buf[(3 * 64 + i) * 12 + s * 4 + 2 * c + 1] = clock64();
+                if (tl_on2 && k == 0 && t < 64) tl_buf[(3 * 64 + t) * 12 + s * 4 + 2 * c + 1] = clock64();
 #endif
               }
               if (!ok) continue;
@@ -608,149 +638,6 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
       }
       __syncwarp();
-    } else if (!kSharedS && warp == 8) {
-      // ==================================================================
-      // MMA issuer (converged warp, one elected lane issues; descriptors are
-      // (hi, lo) pairs of which only the start address in `lo` changes)
-      // ==================================================================
-      const bool leader = elect_one() != 0;
-      bool ok = true;
-      constexpr uint32_t kHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
-      constexpr uint32_t kLoK = (16u >> 4) << 16;
-      constexpr uint32_t kLoV = (static_cast<uint32_t>(kBlockBytes) >> 4) << 16;  // LBO = one block for MN-major V
-      const uint32_t q_lo = (smem_u32(s_q) >> 4) | kLoK;
-      const uint32_t k_lo = (smem_u32(s_kv) >> 4) | kLoK;
-      const uint32_t v_lo = (smem_u32(s_kv) >> 4) | kLoV;
-      auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
-
-      auto issue_s = [&](int s, uint32_t st) {
-        const uint32_t qa = q_lo + s * (kTileBytes >> 4);
-        const uint32_t ka = k_lo + st * (kTileBytes >> 4);
-        const uint32_t ts = tmem_base + s * kTileN;
-#pragma unroll
-        for (int i = 0; i < kDB * 4; ++i) {
-          const uint32_t o = (i >> 2) * (kBlockBytes >> 4) + (i & 3) * 2;  // 32 bytes per 16-element k step
-          if (leader) {
-            if (i == 0) umma_ss_first(ts, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
-            else umma_ss_acc(ts, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
-          }
-        }
-        if (leader) umma_commit(&bars[kSFull + s]);
-      };
-      // piece c of O_s (+)= P_s * V(stage st); the last piece signals o_done
-      auto issue_pv = [&](int s, uint32_t st, int c, bool accumulate) {
-        const int kk0 = (c == 0) ? 0 : 2 * kPSplit;  // 16-key steps [kk0, kk1)
-        const int kk1 = (c == kPPieces - 1) ? kTileN / 16 : 2 * kPSplit;
-        const uint32_t va = v_lo + st * (kTileBytes >> 4);
-        const uint32_t tp = tmem_base + s * kTileN;  // P: packed 16-bit pairs, 8 columns per 16 keys
-        const uint32_t to = tmem_base + 256 + s * 128;
-#pragma unroll
-        for (int kk = 0; kk < kTileN / 16; ++kk) {
-          if (kk < kk0 || kk >= kk1) continue;
-          if (leader) {
-            if (kk == kk0) umma_ts(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO, accumulate ? 1u : 0u);
-            else umma_ts_acc(to, tp + kk * 8, desc(va + kk * (2048 >> 4), kHi), kIdescO);
-          }
-        }
-        if (c == kPPieces - 1 && leader) umma_commit(&bars[kODone + s]);
-      };
-
-      uint32_t tiles[2] = {0u, 0u};  // key tiles finished per slot over the CTA's lifetime (parity of p_full)
-      uint32_t items[2] = {0u, 0u};  // items in which the slot had work (parity of q_full / o_free)
-      uint32_t r = 0;                // K/V ring position, in step with the TMA warp
-      for (int k = 0; ok; ++k) {
-        const int id = next_item(k, ok);
-        if (!ok) { report_p(a.status, 37); break; }
-        if (id < 0) break;
-        const Item it = decode_item(a, id, dynamic && a.order_by_kv_set);
-        const TileList tl = list_of(it, k);
-        if (tl.n_u == 0) {
-          if (leader) release_item(k);
-          continue;
-        }
-#pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          if (tl.nvis[s] > 0 && ok && !(ok = mbar_wait(&bars[kQFull + s], items[s] & 1u, abort_flag)))
-            report_p(a.status, 30);
-        }
-        if (!ok) break;
-        // dense masks: S / PV tiles issued per slot in this item (a prefix needs no counting)
-        [[maybe_unused]] int s_issued[2] = {0, 0};
-        [[maybe_unused]] int pv_done[2] = {0, 0};
-        // was the S just issued for listed tile `idx` the slot's last of the item?
-        auto last_s = [&](int s, int idx) -> bool {
-          if constexpr (kMasked) return ++s_issued[s] == tl.nvis[s];
-          else return idx + 1 == tl.nvis[s];
-        };
-        // first listed K tile
-        if (!(ok = mbar_wait(&bars[kKvFull + r % kStages], (r / kStages) & 1u, abort_flag))) { report_p(a.status, 31); break; }
-        tc_fence_after();
-        {
-          const uint32_t f0 = tl.template flag_at<kMasked>(0);
-#pragma unroll
-          for (int s = 0; s < 2; ++s) {
-            if (f0 & (1u << (2 * s))) {
-              issue_s(s, r % kStages);
-              if (last_s(s, 0) && leader) umma_commit(&bars[kQEmpty + s]);  // the slot's last S of the item
-            }
-          }
-        }
-        if (leader) umma_commit(&bars[kKvEmpty + r % kStages]);
-
-        // Per listed tile i and slot s: PV_s(i) if s visits i, then S_s(i+1) if s visits i+1.  Only K of
-        // the next listed tile is ever needed ahead, so the ring cannot deadlock however sparse a slot's
-        // visits are.
-        for (int i = 0; i < tl.n_u && ok; ++i) {
-          const uint32_t rv = r + 2 * i + 1;  // ring position of V of listed tile i
-          const uint32_t rk = r + 2 * i + 2;  // ring position of K of listed tile i+1
-          const uint32_t stv = rv % kStages, stk = rk % kStages;
-          const uint32_t f = tl.template flag_at<kMasked>(i);
-          const uint32_t fn = (i + 1 < tl.n_u) ? tl.template flag_at<kMasked>(i + 1) : 0u;
-          if (!(ok = mbar_wait(&bars[kKvFull + stv], (rv / kStages) & 1u, abort_flag))) { report_p(a.status, 32); break; }
-          bool k_waited = false;
-#pragma unroll
-          for (int s = 0; s < 2; ++s) {
-            if (!ok) continue;
-            if (f & (1u << (2 * s))) {
-              const bool first_pv = kMasked ? pv_done[s] == 0 : i == 0;
-              if (first_pv && items[s] > 0) {
-                // O_s still holds the previous item's result until its epilogue has read it
-                if (!(ok = mbar_wait(&bars[kOFree + s], (items[s] - 1) & 1u, abort_flag))) { report_p(a.status, 35); continue; }
-              }
-#pragma unroll
-              for (int c = 0; c < kPPieces; ++c) {
-                if (!ok) continue;
-                if (!(ok = mbar_wait(&bars[kPFull + 4 * s + c], tiles[s] & 1u, abort_flag))) { report_p(a.status, 33); continue; }
-                tc_fence_after();
-                issue_pv(s, stv, c, !first_pv || c > 0);
-              }
-              if (!ok) continue;
-              ++tiles[s];
-              if constexpr (kMasked) ++pv_done[s];
-            }
-            if (fn & (1u << (2 * s))) {
-              if (!k_waited) {
-                if (!(ok = mbar_wait(&bars[kKvFull + stk], (rk / kStages) & 1u, abort_flag))) { report_p(a.status, 34); continue; }
-                k_waited = true;
-                tc_fence_after();
-              }
-              issue_s(s, stk);
-              if (last_s(s, i + 1) && leader) umma_commit(&bars[kQEmpty + s]);  // last S of the item for this slot
-            }
-          }
-          if (!ok) break;
-          if (leader) {
-            umma_commit(&bars[kKvEmpty + stv]);
-            if (i + 1 < tl.n_u) umma_commit(&bars[kKvEmpty + stk]);
-          }
-        }
-        r += 2 * tl.n_u;
-#pragma unroll
-        for (int s = 0; s < 2; ++s)
-          if (tl.nvis[s] > 0) ++items[s];
-        if (leader) release_item(k);
-      }
-      __syncwarp();
     }
   } else {
     // ====================================================================
@@ -761,10 +648,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int row = tid & 127;
     const int lane = tid & 31;
     const uint32_t t_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tmem_s = tmem_base + (kSharedS ? 0 : s * kTileN) + t_lane;
-    const uint32_t tmem_p = kSharedS ? tmem_base + 128 + s * 64 + t_lane : tmem_s;  // packed P
+    const uint32_t tmem_s = tmem_base + t_lane;                 // scores (shared by the two slots)
+    const uint32_t tmem_p = tmem_base + 128 + s * 64 + t_lane;  // packed P
     const uint32_t tmem_o = tmem_base + 256 + s * 128 + t_lane;
-    const uint32_t visit_bit = 1u << (2 * s), mixed_bit = 2u << (2 * s);
     const float sl2 = a.scale_log2;
     const int off = a.seq_k - a.seq_q;
     bool ok = true;
@@ -804,15 +690,16 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       float l_run = 0.f;
       int jm = 0;  // key tiles this slot has processed in this item (dense masks; else the loop index)
 
-      const int n_iter = kMasked ? tl.n_u : nvis;
+      const int n_iter = kMasked ? tl.n_t : nvis;
+      [[maybe_unused]] uint32_t pv = 0u, pm = 0u;
       for (int i = 0; i < n_iter; ++i) {
-        uint32_t fl = visit_bit;
-        int kv0 = i * kTileN;
+        bool mixed = false;  // dense masks: the tile needs its mask bytes
         if constexpr (kMasked) {
-          fl = tl.flags[i];
-          if (!(fl & visit_bit)) continue;
-          kv0 = tl.tiles[i] * kTileN;
+          const uint32_t fl = tl.slot_flag_at(s, i, pv, pm);
+          if (!(fl & 1u)) continue;
+          mixed = (fl & 2u) != 0u;
         }
+        const int kv0 = i * kTileN;
         const int j = kMasked ? jm : i;
         P_ACC(acc_c = clock64());
         P_TL(s, j, 0);
@@ -826,11 +713,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int c = 0; c < kTileN / 32; ++c)
           tmem_ld32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
         tc_wait_ld();
-        if constexpr (kSharedS) {
-          // the scores are in registers: the S columns may take the next score tile (either slot's)
-          tc_fence_before();
-          mbar_arrive(&bars[kSFree]);
-        }
+        // the scores are in registers: the S columns may take the next score tile (either slot's)
+        tc_fence_before();
+        mbar_arrive(&bars[kSFree]);
         P_TL(s, j, 2);
         P_ACC(acc_c = clock64(); acc_ld += acc_c - acc_c2);
 
@@ -838,7 +723,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // the diagonal and the ragged last tile need it ----
         const bool tail = kv0 + kTileN > a.seq_k;
         const bool diag = !kMasked && a.causal && (kv0 + kTileN - 1 > q0s + off);
-        if (kMasked && (fl & mixed_bit)) {
+        if (kMasked && mixed) {
           if (!tail && a.mask_vec) {
             const uint4* mp = reinterpret_cast<const uint4*>(mrow + kv0);
 #pragma unroll
@@ -905,11 +790,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         P_TL(s, j, 3);
         P_ACC(acc_c2 = clock64(); acc_max += acc_c2 - acc_c);
         // ---- P = exp2(S*c - m*c) -> 16-bit pairs -> tensor memory ----
-        if constexpr (kSharedS) {
-          // the PV MMAs of this slot's previous tile must have finished reading the P columns
-          if (jt > 0 && !(ok = mbar_wait(&bars[kPFree + s], (jt - 1) & 1u, abort_flag))) { report_p(a.status, 44); break; }
-          tc_fence_after();
-        }
+        // the PV MMAs of this slot's previous tile must have finished reading the P columns
+        if (jt > 0 && !(ok = mbar_wait(&bars[kPFree + s], (jt - 1) & 1u, abort_flag))) { report_p(a.status, 44); break; }
+        tc_fence_after();
         const float mb = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
         const float2 sl2_2 = make_float2(sl2, sl2);
         const float2 nmb_2 = make_float2(-mb, -mb);
@@ -1019,10 +902,12 @@ template <int D, bool BF16, bool kMasked>
 cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                                const CUtensorMap& to, PrefillArgs a,
                                cudaStream_t stream) {
-  constexpr int kStages = (D == 128) ? (kMasked ? 3 : MINFER_ATTN_STAGES128) : 8;
-  // tiles, epilogue staging, barriers and ring heads, (dense masks) the ring's tile lists, alignment slack
-  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 8 * kEpiBytes + 768 +
-                          (kMasked ? kSchedRing * kMaxList * 3 : 0) + 1024;
+  constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
+  // tiles, epilogue staging, barriers and ring heads, (dense masks) the ring's bit planes, alignment slack:
+  // exactly the 227 KB an SM offers for the masked D = 128 form
+  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 8 * kEpiBytes + 512 +
+                          (kMasked ? kMaskRing * (kMaxTiles / 8) * 4 : 0) + 1024;
+  static_assert(smem <= 232448, "shared memory per CTA");
   static bool attr_done[64] = {};
   static int sm_count[64] = {};
   int dev = 0;
