@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define MINFER_ATTN_ABI_VERSION 3
+#define MINFER_ATTN_ABI_VERSION 4
 
 /* element types of q/k/v/out */
 #define MINFER_ATTN_F16  0
@@ -151,6 +151,15 @@ size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t
  * kv_stride[2] is ignored; max_len must be even.  Every cached value is used as
  * (16-bit type)(q * d), the reference's dequant_row_q8_0 (csrc/quants/impl.cpp:
  * 1153-1166), so the result equals the 16-bit path run on the dequantised cache.
+ *
+ * Paged cache (block_table != NULL): the caches are pools of pages,
+ * [n_pages, n_kv_heads, page_size, head_dim]; key j of sequence b lives in page
+ * block_table[b * table_stride + j / page_size] at row j % page_size.
+ * kv_stride[0] is then the stride between PAGES (elements, or bytes for Q8_0),
+ * kv_stride[1] / [2] those of a head / row inside a page, page_size a positive
+ * multiple of 16, max_len <= table_stride * page_size.  Only the table entries
+ * below ceil(lens[b] / page_size) are read.  The reference's cache
+ * (src/minfer/core.py:105-127) is the contiguous special case.
  */
 typedef struct MinferAttnDecodeParams {
   const void*    q;
@@ -172,6 +181,9 @@ typedef struct MinferAttnDecodeParams {
   int32_t chunk;
   float   softmax_scale;
   int32_t kv_format;      /* MINFER_ATTN_KV_16BIT (0) or MINFER_ATTN_KV_Q8_0 */
+  const int32_t* block_table;  /* NULL: contiguous cache; else device int32[batch, table_stride] of page indices */
+  int32_t page_size;      /* keys per page (multiple of 16); ignored without a block table */
+  int32_t table_stride;   /* entries per sequence in block_table */
 } MinferAttnDecodeParams;
 
 int minfer_attn_decode(const MinferAttnDecodeParams* params, void* stream);
@@ -258,6 +270,9 @@ typedef struct MinferRopeParams {
   int32_t style;
   float   freq_base;
   int32_t cache_format;   /* MINFER_ATTN_KV_16BIT (0) or MINFER_ATTN_KV_Q8_0 */
+  const int32_t* block_table;  /* NULL, or the paged cache's int32[batch, table_stride] (see MinferAttnDecodeParams): */
+  int32_t page_size;      /*   row start[b] + l goes to page block_table[b][pos / page_size], row pos % page_size; */
+  int32_t table_stride;   /*   cache_stride[0] is then the stride between pages and page_size may be any value > 0 */
 } MinferRopeParams;
 
 int minfer_attn_rope_append(const MinferRopeParams* params, void* stream);

@@ -230,6 +230,13 @@ int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {
       return MINFER_ATTN_EINVAL;
     if (p->max_len <= 0) return MINFER_ATTN_EINVAL;
     if (p->start == nullptr && (p->start_pos < 0 || p->start_pos + p->seq > p->max_len)) return MINFER_ATTN_EINVAL;
+    if (p->block_table != nullptr) {
+      if (p->page_size <= 0 || p->table_stride <= 0 || (reinterpret_cast<uintptr_t>(p->block_table) & 3) != 0)
+        return MINFER_ATTN_EINVAL;
+      if (static_cast<int64_t>(p->page_size) * p->table_stride < p->max_len) return MINFER_ATTN_EINVAL;
+    }
+  } else if (p->block_table != nullptr) {
+    return MINFER_ATTN_EINVAL;
   }
   if (p->start == nullptr && p->start_pos < 0) return MINFER_ATTN_EINVAL;
   int rc = check_device();
@@ -255,6 +262,9 @@ int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {
   a.start_pos = p->start_pos;
   a.freq_base = p->freq_base;
   a.cache_q8 = cq8 ? 1 : 0;
+  a.block_table = p->block_table;
+  a.page_size = p->block_table != nullptr ? p->page_size : 0;
+  a.table_stride = p->block_table != nullptr ? p->table_stride : 0;
   return cuda_result(launch_rope_append(a, p->dtype == MINFER_ATTN_BF16, p->style == 1, static_cast<cudaStream_t>(stream)));
 }
 
@@ -296,6 +306,11 @@ int minfer_attn_decode(const MinferAttnDecodeParams* p, void* stream) {
   }
   if (!(p->softmax_scale >= 0.f)) return MINFER_ATTN_EINVAL;
   if (p->batch > 65535 || p->n_kv_heads > 65535) return MINFER_ATTN_EUNSUPPORTED;
+  if (p->block_table != nullptr) {
+    if (p->page_size <= 0 || p->page_size % 16 != 0 || p->table_stride <= 0) return MINFER_ATTN_EINVAL;
+    if (static_cast<int64_t>(p->table_stride) * p->page_size < p->max_len) return MINFER_ATTN_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(p->block_table) & 3) != 0) return MINFER_ATTN_EINVAL;
+  }
   int32_t chunk = p->chunk;
   if (chunk == 0) chunk = default_chunk(p->batch, p->n_kv_heads, p->max_len);
   if (chunk < 64 || chunk % 64 != 0) return MINFER_ATTN_EINVAL;
@@ -326,6 +341,9 @@ int minfer_attn_decode(const MinferAttnDecodeParams* p, void* stream) {
   for (int i = 0; i < 3; ++i) a.kv_stride[i] = p->kv_stride[i];
   const float scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->head_dim));
   a.scale_log2 = scale * 1.4426950408889634f;
+  a.block_table = p->block_table;
+  a.page_size = p->block_table != nullptr ? p->page_size : 0;
+  a.table_stride = p->block_table != nullptr ? p->table_stride : 0;
 
   cudaError_t e = launch_decode(a, p->head_dim, p->dtype == MINFER_ATTN_BF16, q8, static_cast<cudaStream_t>(stream));
   return cuda_result(e);

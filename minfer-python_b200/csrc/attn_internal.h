@@ -61,6 +61,8 @@ struct RopeArgs {
   int32_t batch, seq, n_heads, n_kv_heads, head_dim, rotary_dim, start_pos;
   int32_t cache_q8;         // caches hold GGML Q8_0 blocks; cache_stride then in bytes (batch, head), rows contiguous
   float freq_base;
+  const int32_t* block_table;  // paged cache: [batch, table_stride] page indices; cache_stride[0] is then per page
+  int32_t page_size, table_stride;
 };
 cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, bool neox, cudaStream_t stream);
 
@@ -81,6 +83,8 @@ struct DecodeArgs {
   int32_t chunk;    // keys per thread block
   int32_t n_split;  // ceil(max_len / chunk)
   float scale_log2;
+  const int32_t* block_table;  // paged cache: [batch, table_stride] page indices; kv_stride[0] is then per page
+  int32_t page_size, table_stride;
 };
 
 cudaError_t launch_decode(const DecodeArgs& a, int head_dim, bool bf16, bool q8, cudaStream_t stream);

@@ -94,7 +94,9 @@ __device__ __forceinline__ void dequant8(const uint8_t* block, int part, bool li
   *reinterpret_cast<uint4*>(dst) = out;
 }
 
-template <int D, bool BF16, bool Q8>
+// Paged: the caches are pools of pages reached through a.block_table (a separate instantiation, so that the
+// contiguous form keeps its registers).
+template <int D, bool BF16, bool Q8, bool Paged>
 __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(const DecodeArgs a) {
   constexpr int kRowBytes = D * 2;
   constexpr int kTileBytes = kTileKeys * kRowBytes;        // one of K or V, 16-bit
@@ -127,21 +129,29 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
 
   uint8_t* wsm = smem + warp * kWarpBytes;
   const uint32_t wsm_u32 = smem_u32(wsm);
-  const uint8_t* kbase = reinterpret_cast<const uint8_t*>(a.k) +
-                         2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(kvh) * a.kv_stride[1]);
-  const uint8_t* vbase = reinterpret_cast<const uint8_t*>(a.v) +
-                         2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(kvh) * a.kv_stride[1]);
-  const size_t row_stride_bytes = 2 * static_cast<size_t>(a.kv_stride[2]);
+  // Byte offset of the first row of a 16-key tile inside either cache.  Paged caches: the tile lies inside one
+  // page (page_size is a multiple of 16), found through the block table; strides are then those of the pool.
+  // (Everything is recomputed per tile from kernel parameters, which costs no registers between tiles.)
+  auto tile_offset = [&](int key0) -> size_t {
+    constexpr size_t kUnit = Q8 ? 1 : 2;  // Q8_0 strides are in bytes
+    const size_t row_bytes = Q8 ? static_cast<size_t>((D / 32) * 34) : 2 * static_cast<size_t>(a.kv_stride[2]);
+    const size_t head_off = kUnit * static_cast<size_t>(kvh) * a.kv_stride[1];
+    if constexpr (Paged) {
+      const int page = __ldg(a.block_table + static_cast<size_t>(b) * a.table_stride + key0 / a.page_size);
+      return kUnit * static_cast<size_t>(page) * a.kv_stride[0] + head_off + static_cast<size_t>(key0 % a.page_size) * row_bytes;
+    }
+    return kUnit * static_cast<size_t>(b) * a.kv_stride[0] + head_off + static_cast<size_t>(key0) * row_bytes;
+  };
+  const size_t row_stride_bytes = 2 * static_cast<size_t>(a.kv_stride[2]);  // 16-bit caches
 
   auto issue_tile = [&](int i) {  // i-th tile of this warp -> stage i % kStages
     if (i < nt_w) {
       const int key0 = c0 + (warp + i * kWarps) * kTileKeys;
+      const size_t toff = tile_offset(key0);
       if constexpr (Q8) {
         // strides of a Q8_0 cache are in bytes; rows are contiguous
-        const uint8_t* kq = reinterpret_cast<const uint8_t*>(a.k) + static_cast<size_t>(b) * a.kv_stride[0] +
-                            static_cast<size_t>(kvh) * a.kv_stride[1] + static_cast<size_t>(key0) * kQRowBytes;
-        const uint8_t* vq = reinterpret_cast<const uint8_t*>(a.v) + static_cast<size_t>(b) * a.kv_stride[0] +
-                            static_cast<size_t>(kvh) * a.kv_stride[1] + static_cast<size_t>(key0) * kQRowBytes;
+        const uint8_t* kq = reinterpret_cast<const uint8_t*>(a.k) + toff;
+        const uint8_t* vq = reinterpret_cast<const uint8_t*>(a.v) + toff;
         uint8_t* dst_k = wsm + (i % kStages) * 2 * kQTileBytes;
         uint8_t* dst_v = dst_k + kQTileBytes;
         // bytes of live rows in this tile (rows beyond the sequence are neither read nor used)
@@ -165,11 +175,10 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
         const int idx = t * 32 + lane;
         const int row = idx / kChunksPerRow;
         const int chunk = idx % kChunksPerRow;
-        const int key = key0 + row;
-        const bool pred = key < c1;
-        const size_t goff = static_cast<size_t>(pred ? key : c0) * row_stride_bytes + chunk * 16;
-        cp_async_16(dst_k + swz<D>(row, chunk), kbase + goff, pred);
-        cp_async_16(dst_v + swz<D>(row, chunk), vbase + goff, pred);
+        const bool pred = key0 + row < c1;
+        const size_t goff = toff + static_cast<size_t>(pred ? row : 0) * row_stride_bytes + chunk * 16;
+        cp_async_16(dst_k + swz<D>(row, chunk), reinterpret_cast<const uint8_t*>(a.k) + goff, pred);
+        cp_async_16(dst_v + swz<D>(row, chunk), reinterpret_cast<const uint8_t*>(a.v) + goff, pred);
       }
     }
     cp_async_commit();
@@ -392,8 +401,8 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
   else *reinterpret_cast<__half*>(op) = __float2half_rn(r);
 }
 
-template <int D, bool BF16, bool Q8>
-cudaError_t launch_one(const DecodeArgs& a, cudaStream_t stream) {
+template <int D, bool BF16, bool Q8, bool Paged>
+cudaError_t launch_paged(const DecodeArgs& a, cudaStream_t stream) {
   constexpr int kRaw = Q8 ? kTileKeys * (D / 32) * 34 : kTileKeys * D * 2;
   constexpr int smem = kWarps * (kStages * 2 * kRaw + (Q8 ? kTileKeys * D * 2 : 0));
   static_assert(smem / kWarps >= 16 * D * 4 + 128, "the per-warp region also holds the fp32 merge buffer");
@@ -402,16 +411,21 @@ cudaError_t launch_one(const DecodeArgs& a, cudaStream_t stream) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 64 && !attr_done[dev]) {
-    e = cudaFuncSetAttribute(decode_split_kernel<D, BF16, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(decode_split_kernel<D, BF16, Q8, Paged>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
   dim3 grid(a.n_split, a.n_kv_heads, a.batch);
-  decode_split_kernel<D, BF16, Q8><<<grid, kWarps * 32, smem, stream>>>(a);
+  decode_split_kernel<D, BF16, Q8, Paged><<<grid, kWarps * 32, smem, stream>>>(a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   decode_combine_kernel<D, BF16><<<dim3(a.n_heads, a.batch), D, 0, stream>>>(a);
   return cudaGetLastError();
+}
+
+template <int D, bool BF16, bool Q8>
+cudaError_t launch_one(const DecodeArgs& a, cudaStream_t stream) {
+  return a.block_table != nullptr ? launch_paged<D, BF16, Q8, true>(a, stream) : launch_paged<D, BF16, Q8, false>(a, stream);
 }
 
 }  // namespace

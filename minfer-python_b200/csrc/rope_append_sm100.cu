@@ -126,6 +126,14 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
   const int b = static_cast<int>(token / a.seq);
   const int l = static_cast<int>(token % a.seq);
   const int pos = (a.start ? a.start[b] : a.start_pos) + l;
+  // where the row of position `pos` starts inside a cache, in units of the cache strides, head offset excluded:
+  // contiguous [batch][head][row] caches, or a pool of pages reached through the block table
+  size_t cb = static_cast<size_t>(b);
+  int crow = pos;
+  if (a.block_table != nullptr) {
+    cb = static_cast<size_t>(a.block_table[static_cast<size_t>(b) * a.table_stride + pos / a.page_size]);
+    crow = pos % a.page_size;
+  }
 
   float cs[8], sn[8];
   if (rotate) {
@@ -193,8 +201,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
     for (int h = 0; h < a.n_kv_heads; ++h) {
       const uint8_t* row = base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
       if (a.cache_q8) {  // cache strides in bytes, rows contiguous
-        uint8_t* qrow = reinterpret_cast<uint8_t*>(a.k_cache) + static_cast<size_t>(b) * a.cache_stride[0] +
-                        static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(pos) * q_row_bytes;
+        uint8_t* qrow = reinterpret_cast<uint8_t*>(a.k_cache) + cb * a.cache_stride[0] +
+                        static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(crow) * q_row_bytes;
         float ox[8], oy[8];
         rot8f(row + co, row + co2, ox, oy);
         round16<BF16>(ox);
@@ -206,7 +214,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
         continue;
       }
       uint8_t* drow = a.k_cache != nullptr
-                          ? reinterpret_cast<uint8_t*>(a.k_cache) + 2 * (static_cast<size_t>(b) * a.cache_stride[0] + static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(pos) * a.cache_stride[2])
+                          ? reinterpret_cast<uint8_t*>(a.k_cache) + 2 * (cb * a.cache_stride[0] + static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(crow) * a.cache_stride[2])
                           : const_cast<uint8_t*>(row);
       rot8(row + co, row + co2, drow + co, drow + co2);
     }
@@ -217,8 +225,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
     for (int h = 0; h < a.n_kv_heads; ++h) {
       const uint8_t* row = base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
       if (a.cache_q8) {
-        uint8_t* qrow = reinterpret_cast<uint8_t*>(a.v_cache) + static_cast<size_t>(b) * a.cache_stride[0] +
-                        static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(pos) * q_row_bytes;
+        uint8_t* qrow = reinterpret_cast<uint8_t*>(a.v_cache) + cb * a.cache_stride[0] +
+                        static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(crow) * q_row_bytes;
         float x[8];
         unpack8<BF16>(*reinterpret_cast<const uint4*>(row + co), x);
         store_q8_quarter(x, qrow + (c >> 2) * 34, c & 3);
@@ -228,7 +236,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
         }
         continue;
       }
-      uint8_t* drow = reinterpret_cast<uint8_t*>(a.v_cache) + 2 * (static_cast<size_t>(b) * a.cache_stride[0] + static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(pos) * a.cache_stride[2]);
+      uint8_t* drow = reinterpret_cast<uint8_t*>(a.v_cache) + 2 * (cb * a.cache_stride[0] + static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(crow) * a.cache_stride[2]);
       *reinterpret_cast<uint4*>(drow + co) = *reinterpret_cast<const uint4*>(row + co);
       if (c2 >= 0) *reinterpret_cast<uint4*>(drow + co2) = *reinterpret_cast<const uint4*>(row + co2);
     }

@@ -1,8 +1,8 @@
 """Dispatch facade with the reference's shape (src/minfer/kernels/__init__.py:2-18).
 
 Only the attention path's attributes exist: `flash_attn`, `il_rope` and `neox_rope`
-keep the reference's signatures; `flash_attn_causal`, `flash_attn_decode` and
-`rope_kv_append` are additions.
+keep the reference's signatures; `flash_attn_causal`, `flash_attn_decode` (also over a
+Q8_0 or a paged cache) and `rope_kv_append` are additions.
 """
 
 
@@ -12,6 +12,9 @@ class KernelBackend:
             from .torch_ext import flash_attn, flash_attn_causal, flash_attn_decode
             from .torch_ext import il_rope, neox_rope, rope_kv_append
             from .torch_ext import flash_attn_decode_q8, rope_kv_append_q8
+            from .torch_ext import flash_attn_decode_paged, rope_kv_append_paged
+            self.flash_attn_decode_paged = flash_attn_decode_paged
+            self.rope_kv_append_paged = rope_kv_append_paged
             self.flash_attn_decode_q8 = flash_attn_decode_q8
             self.rope_kv_append_q8 = rope_kv_append_q8
             self.il_rope = il_rope

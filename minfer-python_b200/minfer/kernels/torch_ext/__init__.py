@@ -8,3 +8,4 @@ from . import _lib  # noqa: F401  (dlopen first: ops need the entry points)
 from .ops import flash_attn, flash_attn_causal, flash_attn_decode  # noqa: F401
 from .ops import il_rope, neox_rope, rope_kv_append  # noqa: F401
 from .ops import flash_attn_decode_q8, rope_kv_append_q8  # noqa: F401
+from .ops import flash_attn_decode_paged, rope_kv_append_paged  # noqa: F401

@@ -78,6 +78,9 @@ class DecodeParams(ctypes.Structure):
         ("chunk", ctypes.c_int32),
         ("softmax_scale", ctypes.c_float),
         ("kv_format", ctypes.c_int32),
+        ("block_table", ctypes.c_void_p),
+        ("page_size", ctypes.c_int32),
+        ("table_stride", ctypes.c_int32),
     ]
 
 
@@ -104,6 +107,9 @@ class RopeParams(ctypes.Structure):
         ("style", ctypes.c_int32),
         ("freq_base", ctypes.c_float),
         ("cache_format", ctypes.c_int32),
+        ("block_table", ctypes.c_void_p),
+        ("page_size", ctypes.c_int32),
+        ("table_stride", ctypes.c_int32),
     ]
 
 

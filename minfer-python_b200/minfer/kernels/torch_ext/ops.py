@@ -34,6 +34,11 @@ _DEFS = {
                       "Tensor(a!) k_cache, Tensor(a!) v_cache, Tensor start) -> ()",
     # GGML Q8_0 KV cache: uint8 tensors [B, Hkv, Lmax, head_dim / 32 * 34]
     "flash_attn_decode_q8": "(Tensor q, Tensor k_cache, Tensor v_cache, Tensor lens, Tensor(a!) out) -> ()",
+    # paged KV cache: pools [n_pages, Hkv, page_size, D] reached through block_table int32 [B, max_pages]
+    "flash_attn_decode_paged": "(Tensor q, Tensor k_pages, Tensor v_pages, Tensor block_table, Tensor lens, "
+                               "Tensor(a!) out) -> ()",
+    "rope_kv_append_paged": "(int rotary_dim, float freq_base, int style, Tensor(a!) q, Tensor k, Tensor v, "
+                            "Tensor(a!) k_pages, Tensor(a!) v_pages, Tensor block_table, Tensor start) -> ()",
     "rope_kv_append_q8": "(int rotary_dim, float freq_base, int style, Tensor(a!) q, Tensor k, Tensor v, "
                          "Tensor(a!) k_cache, Tensor(a!) v_cache, Tensor start) -> ()",
 }
@@ -165,7 +170,27 @@ def _flash_attn_decode_cuda(q, k_cache, v_cache, lens, out) -> None:
     _decode_call(q, k_cache, v_cache, lens, out, _lib.KV_16BIT)
 
 
-def _decode_call(q, k_cache, v_cache, lens, out, kv_format) -> None:
+def _flash_attn_decode_paged_cuda(q, k_pages, v_pages, block_table, lens, out) -> None:
+    torch._check(q.is_cuda and out.is_cuda and q.dim() == 4 and out.dim() == 4 and q.shape == out.shape,
+                 lambda: "q/out must be CUDA [B, H, 1, D] tensors")
+    torch._check(q.size(2) == 1, lambda: "decode takes one query token per sequence")
+    torch._check(q.dtype in (torch.float16, torch.bfloat16) and out.dtype == q.dtype, lambda: "q/out must be float16 or bfloat16")
+    torch._check(k_pages.is_cuda and v_pages.is_cuda and k_pages.dim() == 4 and v_pages.dim() == 4,
+                 lambda: "the page pools must be CUDA [n_pages, n_kv_heads, page_size, D] tensors")
+    torch._check(k_pages.dtype == q.dtype and v_pages.dtype == q.dtype, lambda: "the page pools must have q's dtype")
+    torch._check(k_pages.shape == v_pages.shape and k_pages.stride() == v_pages.stride(),
+                 lambda: "the page pools must share shape and strides")
+    torch._check(k_pages.size(3) == q.size(3) and k_pages.stride(-1) == 1 and q.stride(-1) == 1 and out.stride(-1) == 1,
+                 lambda: "head_dim mismatch or innermost stride not 1")
+    torch._check(k_pages.size(2) % 16 == 0, lambda: "page_size must be a multiple of 16")
+    torch._check(q.size(1) % k_pages.size(1) == 0, lambda: "n_heads must be a multiple of n_kv_heads")
+    torch._check(block_table.is_cuda and block_table.dtype == torch.int32 and block_table.dim() == 2 and
+                 block_table.is_contiguous() and block_table.size(0) == q.size(0),
+                 lambda: "block_table must be a contiguous CUDA int32 [B, max_pages] tensor")
+    _decode_call(q, k_pages, v_pages, lens, out, _lib.KV_16BIT, block_table)
+
+
+def _decode_call(q, k_cache, v_cache, lens, out, kv_format, block_table=None) -> None:
     torch._check(lens.is_cuda and lens.device == q.device, lambda: "lens must be on the same CUDA device")
     torch._check(lens.dtype == torch.int32 and lens.dim() == 1 and lens.is_contiguous(),
                  lambda: "lens must be a contiguous int32 vector")
@@ -175,6 +200,10 @@ def _decode_call(q, k_cache, v_cache, lens, out, kv_format) -> None:
     p.lens, p.out = lens.data_ptr(), out.data_ptr()
     p.batch, p.n_heads, p.n_kv_heads = q.size(0), q.size(1), k_cache.size(1)
     p.max_len, p.head_dim = k_cache.size(2), q.size(3)
+    if block_table is not None:
+        p.block_table = block_table.data_ptr()
+        p.page_size, p.table_stride = k_cache.size(2), block_table.size(1)
+        p.max_len = p.page_size * p.table_stride
     p.dtype = _dtype_tag(q)
     p.chunk = 0
     p.softmax_scale = 0.0
@@ -226,7 +255,14 @@ def _rope_kv_append_q8_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_ca
     _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start, q8=True)
 
 
-def _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start, q8=False) -> None:
+def _rope_kv_append_paged_cuda(rotary_dim, freq_base, style, q, k, v, k_pages, v_pages, block_table, start) -> None:
+    torch._check(block_table.is_cuda and block_table.dtype == torch.int32 and block_table.dim() == 2 and
+                 block_table.is_contiguous() and block_table.size(0) == q.size(0),
+                 lambda: "block_table must be a contiguous CUDA int32 [B, max_pages] tensor")
+    _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_pages, v_pages, start, block_table=block_table)
+
+
+def _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, start, q8=False, block_table=None) -> None:
     torch._check(q.is_cuda and k.is_cuda and v.is_cuda and k_cache.is_cuda and v_cache.is_cuda and start.is_cuda,
                  lambda: "all tensors must be on CUDA")
     torch._check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and k_cache.dim() == 4 and v_cache.dim() == 4,
@@ -240,7 +276,8 @@ def _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache
     torch._check(k.shape == v.shape and k.stride() == v.stride(), lambda: "k and v must share shape and strides")
     torch._check(k_cache.shape == v_cache.shape and k_cache.stride() == v_cache.stride(),
                  lambda: "the caches must share shape and strides")
-    torch._check(q.size(0) == k.size(0) == k_cache.size(0) and q.size(1) == k.size(1), lambda: "batch / seq mismatch")
+    torch._check(q.size(0) == k.size(0) and (block_table is not None or k.size(0) == k_cache.size(0)) and
+                 q.size(1) == k.size(1), lambda: "batch / seq mismatch")
     torch._check(k.size(2) == k_cache.size(1) and q.size(3) == k.size(3), lambda: "head count / head_dim mismatch")
     torch._check(q8 or k.size(3) == k_cache.size(3), lambda: "head_dim mismatch")
     torch._check(q.stride(-1) == 1 and k.stride(-1) == 1 and k_cache.stride(-1) == 1, lambda: "innermost stride must be 1")
@@ -253,6 +290,10 @@ def _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache
         p.q_stride[i], p.kv_stride[i], p.cache_stride[i] = q.stride(i), k.stride(i), k_cache.stride(i)
     p.batch, p.seq, p.n_heads, p.n_kv_heads, p.head_dim = q.size(0), q.size(1), q.size(2), k.size(2), q.size(3)
     p.rotary_dim, p.start_pos, p.max_len, p.freq_base = rotary_dim, 0, k_cache.size(2), freq_base
+    if block_table is not None:
+        p.block_table = block_table.data_ptr()
+        p.page_size, p.table_stride = k_cache.size(2), block_table.size(1)
+        p.max_len = p.page_size * p.table_stride
     p.dtype, p.style = _dtype_tag(q), style
     p.cache_format = _lib.KV_Q8_0 if q8 else _lib.KV_16BIT
     _rope_call(p, q.device)
@@ -262,10 +303,12 @@ _library.impl("il_rope", _il_rope_cuda, "CUDA")
 _library.impl("neox_rope", _neox_rope_cuda, "CUDA")
 _library.impl("rope_kv_append", _rope_kv_append_cuda, "CUDA")
 _library.impl("rope_kv_append_q8", _rope_kv_append_q8_cuda, "CUDA")
+_library.impl("rope_kv_append_paged", _rope_kv_append_paged_cuda, "CUDA")
 _library.impl("flash_attn_decode_q8", _flash_attn_decode_q8_cuda, "CUDA")
 _library.impl("flash_attn", _flash_attn_cuda, "CUDA")
 _library.impl("flash_attn_causal", _flash_attn_causal_cuda, "CUDA")
 _library.impl("flash_attn_decode", _flash_attn_decode_cuda, "CUDA")
+_library.impl("flash_attn_decode_paged", _flash_attn_decode_paged_cuda, "CUDA")
 
 
 def flash_attn(
@@ -298,6 +341,16 @@ def flash_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     [B, n_kv_heads, max_len, D], lens int32 [B]; sequence b attends keys [0, lens[b]).
     """
     return torch.ops.minfer.flash_attn_decode.default(q, k_cache, v_cache, lens, out)
+
+
+def flash_attn_decode_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                            lens: torch.Tensor, out: torch.Tensor):
+    """
+    flash_attn_decode over a paged KV cache: pools [n_pages, n_kv_heads, page_size, D] (page_size a multiple
+    of 16), block_table int32 [B, max_pages]; key j of sequence b is row j % page_size of page
+    block_table[b, j // page_size].  Only the entries below ceil(lens[b] / page_size) are read.
+    """
+    return torch.ops.minfer.flash_attn_decode_paged.default(q, k_pages, v_pages, block_table, lens, out)
 
 
 def il_rope(rotary_dim: int, start_pos: int, freq_base: float, x: torch.Tensor):
@@ -333,6 +386,15 @@ def flash_attn_decode_q8(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     return torch.ops.minfer.flash_attn_decode_q8.default(q, k_cache, v_cache, lens, out)
 
 
+def rope_kv_append_paged(rotary_dim: int, freq_base: float, style: int, q: torch.Tensor, k: torch.Tensor,
+                         v: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                         start: torch.Tensor):
+    """rope_kv_append into a paged cache: pools [n_pages, Hkv, page_size, D], block_table int32 [B, max_pages];
+    position p of sequence b goes to row p % page_size of page block_table[b, p // page_size]."""
+    return torch.ops.minfer.rope_kv_append_paged.default(rotary_dim, freq_base, style, q, k, v, k_pages, v_pages,
+                                                         block_table, start)
+
+
 def rope_kv_append_q8(rotary_dim: int, freq_base: float, style: int, q: torch.Tensor, k: torch.Tensor,
                       v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, start: torch.Tensor):
     """rope_kv_append into GGML Q8_0 caches: the rows the 16-bit cache would get, quantised block by block."""
@@ -345,6 +407,15 @@ def _(q, k_cache, v_cache, lens, out):
     torch._check(k_cache.dtype == torch.uint8 and v_cache.dtype == torch.uint8)
     torch._check(lens.dtype == torch.int32)
     torch._check(q.device.type == "cuda")
+
+
+@torch.library.register_fake("minfer::rope_kv_append_paged")
+def _(rotary_dim, freq_base, style, q, k, v, k_pages, v_pages, block_table, start):
+    torch._check(q.dtype in (torch.float16, torch.bfloat16))
+    torch._check(k.dtype == q.dtype and v.dtype == q.dtype and k_pages.dtype == q.dtype and v_pages.dtype == q.dtype)
+    torch._check(start.dtype == torch.int32 and block_table.dtype == torch.int32)
+    torch._check(q.device.type == "cuda")
+    torch._check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and k_pages.dim() == 4 and v_pages.dim() == 4)
 
 
 @torch.library.register_fake("minfer::rope_kv_append_q8")
@@ -401,6 +472,16 @@ def _(q, k, v, out):
     torch._check(k.dtype == q.dtype and v.dtype == q.dtype and out.dtype == q.dtype)
     torch._check(q.device.type == "cuda")
     torch._check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and out.dim() == 4)
+
+
+@torch.library.register_fake("minfer::flash_attn_decode_paged")
+def _(q, k_pages, v_pages, block_table, lens, out):
+    torch._check(q.dtype in (torch.float16, torch.bfloat16))
+    torch._check(k_pages.dtype == q.dtype and v_pages.dtype == q.dtype and out.dtype == q.dtype)
+    torch._check(lens.dtype == torch.int32 and block_table.dtype == torch.int32)
+    torch._check(q.device.type == "cuda")
+    torch._check(q.dim() == 4 and k_pages.dim() == 4 and v_pages.dim() == 4 and out.dim() == 4)
+    torch._check(lens.dim() == 1 and block_table.dim() == 2)
 
 
 @torch.library.register_fake("minfer::flash_attn_decode")

@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     from minfer.kernels.torch_ext import _lib
     for s in declared_symbols():
         assert hasattr(_lib.lib, s), f"{s} declared in the header but not exported"
-    assert _lib.lib.minfer_attn_abi_version() == 3
+    assert _lib.lib.minfer_attn_abi_version() == 4
     assert set(_lib.EXPORTS) <= set(declared_symbols())
 
 

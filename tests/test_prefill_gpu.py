@@ -91,6 +91,27 @@ def test_block_sparse_mask_with_empty_tiles_and_rows(kerns, H, Hkv):
     assert torch.count_nonzero(got[:, :, 256:384]) == 0
 
 
+@pytest.mark.parametrize("D", [128, 64])
+def test_sparse_mask_over_many_key_tiles(kerns, D):
+    """70 key tiles (three 32-tile groups of the kernel's tile flags): a band that leaves whole groups
+    unvisited, query tiles that see far-away groups only or as well, rows that see nothing, and query
+    heads of one kv head that fall into different work items (odd GQA group)."""
+    B, H, Hkv, L = 1, 3, 1, 70 * 128 - 37
+    q, k, v = seeded_qkv(91 + D, B, H, Hkv, L, L, D, torch.float16)
+    rows = torch.arange(L)[:, None]
+    cols = torch.arange(L)[None, :]
+    m = (cols - rows).abs() <= 120                                                        # band around the diagonal
+    m[128:256] = (cols >= 66 * 128 + 5) & (cols < 69 * 128 + 77) & ((rows[128:256] + cols) % 3 != 0)  # last group only
+    m[300:310] = False                                                                    # rows without any visible key
+    m[384:512] |= cols < 40                                                               # group 0 twice
+    m[5000:5128] |= (cols < 130) | (cols >= L - 200)                                      # groups 0, 1 and 2 for one query tile
+    mask = m[None, None].expand(B, 1, L, L).contiguous()
+    want = O.attention_f64(q, k, v, mask=mask)
+    got = run_masked(kerns, q, k, v, mask)
+    check_close(got, want, f"sparse 70 tiles D={D}")
+    assert torch.count_nonzero(got[:, :, 300:310]) == 0
+
+
 def test_dense_mask_without_workspace_matches(kerns):
     """Through the C ABI: the same masked call with and without the tile-class workspace."""
     import ctypes
