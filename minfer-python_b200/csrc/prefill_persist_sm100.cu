@@ -709,32 +709,10 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tc_fence_after();
 
         uint32_t sr[kTileN];
-#ifdef MINFER_ATTN_SPLIT_LD
-        // two loads, wait, two more loads in flight under the first half's row maximum
-        const bool plain_tile = !(kMasked && mixed) && !(kv0 + kTileN > a.seq_k) &&
-                                !(!kMasked && a.causal && (kv0 + kTileN - 1 > q0s + off));
-        float hx0 = -INFINITY, hx1 = -INFINITY, hx2 = -INFINITY, hx3 = -INFINITY;
-        tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
-        tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
-        tc_wait_ld();
-        tmem_ld32(tmem_s + 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[64]));
-        tmem_ld32(tmem_s + 96, *reinterpret_cast<uint32_t(*)[32]>(&sr[96]));
-        if (plain_tile) {
-#pragma unroll
-          for (int c = 0; c < kTileN / 2; c += 8) {
-            hx0 = fmax3(hx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
-            hx1 = fmax3(hx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
-            hx2 = fmax3(hx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
-            hx3 = fmax3(hx3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
-          }
-        }
-        tc_wait_ld();
-#else
 #pragma unroll
         for (int c = 0; c < kTileN / 32; ++c)
           tmem_ld32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
         tc_wait_ld();
-#endif
         // the scores are in registers: the S columns may take the next score tile (either slot's)
         tc_fence_before();
         mbar_arrive(&bars[kSFree]);
@@ -772,28 +750,15 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
 
         // ---- row maximum; move the reference only when it lags by > 2^8 ----
-        float mx = m_ref;
-#ifdef MINFER_ATTN_EXPERIMENT_SKIP_MAX
-        if (j == 0)
-#endif
-        {
-#ifdef MINFER_ATTN_SPLIT_LD
-          float mx0 = hx0, mx1 = hx1, mx2 = hx2, mx3 = hx3;
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-          for (int c = 0; c < kTileN; c += 8) {
-            if (plain_tile && c < kTileN / 2) continue;
-#else
-          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-          for (int c = 0; c < kTileN; c += 8) {
-#endif
-            mx0 = fmax3(mx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
-            mx1 = fmax3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
-            mx2 = fmax3(mx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
-            mx3 = fmax3(mx3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
-          }
-          mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        for (int c = 0; c < kTileN; c += 8) {
+          mx0 = fmax3(mx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+          mx2 = fmax3(mx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
+          mx3 = fmax3(mx3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
         }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         const bool move = (mx != -INFINITY) && (m_ref == -INFINITY || (mx - m_ref) * sl2 > kRescaleThreshold);
         if (__any_sync(0xFFFFFFFFu, move)) {
           const float alpha = (move && m_ref != -INFINITY) ? ex2_approx((m_ref - mx) * sl2) : 1.f;
