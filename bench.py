@@ -10,7 +10,9 @@ A step is one pass of the hot path over one batch of synthetic input:
     (4*B*H*L^2*D / 2 floating-point operations per step);
   * `e2e`: the same call through KernelBackend("torch_ext").flash_attn_causal
     with pinned HOST buffers, host->device and device->host copies inside the
-    timed region;
+    timed region; consecutive steps overlap their uploads, launches and
+    downloads (three streams, two sets of device buffers), and the figure
+    without any overlap is reported beside it (`ms_per_step_one_stream`);
   * `decode`: the split-KV decode kernel over a padded KV cache (batch 64,
     32/8 heads, head_dim 128, lengths uniform in [512, 8192]), GB/s of live
     KV-cache bytes;
@@ -217,7 +219,37 @@ def run_gpu_arm(args):
     def step():
         kerns.flash_attn_causal(q, k, v, out)
 
-    def step_e2e():
+    # End-to-end leg: every step copies its inputs from pinned host memory, runs the call and reads the result
+    # back.  Copies and kernels of consecutive steps overlap the way a serving loop would overlap them: an
+    # upload stream, the stream the library launches on, and a download stream, over two sets of device buffers.
+    # Every step's three uploads, its launch and its download are inside the timed region.
+    s_in, s_run, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    bufs = [(q, k, v, out), (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v), torch.empty_like(out))]
+    ev_in = [torch.cuda.Event(), torch.cuda.Event()]    # inputs of the set have arrived
+    ev_run = [torch.cuda.Event(), torch.cuda.Event()]   # the call on the set has finished
+    ev_out = [torch.cuda.Event(), torch.cuda.Event()]   # the set's result has reached the host
+
+    def step_e2e(i):
+        bq, bk, bv, bo = bufs[i & 1]
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(ev_run[i & 1])          # the call two steps ago has read these inputs
+            bq.copy_(hq, non_blocking=True)
+            bk.copy_(hk, non_blocking=True)
+            bv.copy_(hv, non_blocking=True)
+            ev_in[i & 1].record(s_in)
+        with torch.cuda.stream(s_run):
+            s_run.wait_event(ev_in[i & 1])
+            if i >= 2:
+                s_run.wait_event(ev_out[i & 1])         # the result two steps ago has left this buffer
+            kerns.flash_attn_causal(bq, bk, bv, bo)
+            ev_run[i & 1].record(s_run)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_run[i & 1])
+            hout.copy_(bo, non_blocking=True)
+            ev_out[i & 1].record(s_out)
+
+    def step_e2e_serial():
         q.copy_(hq, non_blocking=True)
         k.copy_(hk, non_blocking=True)
         v.copy_(hv, non_blocking=True)
@@ -245,18 +277,31 @@ def run_gpu_arm(args):
     check_status(dev)
 
     # ---- end-to-end timing (host buffers) ----
-    for _ in range(2):
-        step_e2e()
-    barrier(world)
+    e2e_steps = min(args.steps, 100)  # each step moves 336 MB over PCIe; 100 steps are ~0.4 s
+    for i in range(4):
+        step_e2e(i)
     torch.cuda.synchronize()
-    e2e_steps = min(args.steps, 100)  # each step moves 336 MB over PCIe; 100 steps are ~0.7 s
-    e0.record()
-    for _ in range(e2e_steps):
-        step_e2e()
-    e1.record()
+    barrier(world)
+    e0.record(s_run)
+    for i in range(e2e_steps):
+        step_e2e(i)
+    s_run.wait_stream(s_out)
+    s_run.wait_stream(s_in)
+    e1.record(s_run)
     torch.cuda.synchronize()
     barrier(world)
     ms_e2e = max_over_ranks(e0.elapsed_time(e1), world, dev) / e2e_steps
+    check_status(dev)
+    # the same without overlap between steps (one stream), for reference
+    for _ in range(2):
+        step_e2e_serial()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(min(e2e_steps, 30)):
+        step_e2e_serial()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_e2e_serial = max_over_ranks(e0.elapsed_time(e1), world, dev) / min(e2e_steps, 30)
 
     # ---- decode leg (per GPU; the same shard on every rank) ----
     d = DECODE
@@ -317,7 +362,8 @@ def run_gpu_arm(args):
             "clocks": clocks,
             "e2e": {"value": flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes, "ms_per_step": ms_e2e,
-                    "steps": e2e_steps},
+                    "steps": e2e_steps, "overlap": "uploads, launches and downloads of consecutive steps overlap "
+                    "(three streams, two device buffer sets)", "ms_per_step_one_stream": ms_e2e_serial},
             "gpu_launches": args.steps,
             "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
                          "frac": per_gpu_tflops / tensor_peak, "traffic": traffic.get("prefill"),
