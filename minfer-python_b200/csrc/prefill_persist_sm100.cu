@@ -841,28 +841,30 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int row0 = q0s + (warp & 3) * 32;  // first row of this warp
         auto pick = [&](int i) { return a.out_pos[0] == i ? it.b : (a.out_pos[1] == i ? heads : row0); };
         const int c1 = pick(1), c2 = pick(2), c3 = pick(3);
-        uint32_t o[D];
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) tmem_ld32(tmem_o + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[c * 32]));
-        tc_wait_ld();
-        tc_fence_before();
-        mbar_arrive(&bars[kOFree + s]);  // the MMA warp may overwrite O_s for the next item
-        P_ACC(acc_el += clock64() - acc_c2);
+        // 64 columns at a time: load, pack, hand to the TMA unit; the next 64 columns are loaded while the
+        // unit reads the staging buffer
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
+          uint32_t o[64];
+          tmem_ld32(tmem_o + h * 64, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
+          tmem_ld32(tmem_o + h * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&o[32]));
+          tc_wait_ld();
+          if (h == D / 64 - 1) {
+            tc_fence_before();
+            mbar_arrive(&bars[kOFree + s]);  // the MMA warp may overwrite O_s for the next item
+            P_ACC(acc_el += clock64() - acc_c2);
+          }
+          uint32_t v[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            v[e] = pack2<BF16>(__uint_as_float(o[2 * e]) * inv, __uint_as_float(o[2 * e + 1]) * inv);
           // the staging buffer is free once the previous box (this pass's predecessor, or the last
           // one of the previous item) has been read by the TMA unit
           if (lane == 0) bulk_wait_read();
           __syncwarp();
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            uint32_t v[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              v[e] = pack2<BF16>(__uint_as_float(o[h * 64 + c * 8 + 2 * e]) * inv,
-                                 __uint_as_float(o[h * 64 + c * 8 + 2 * e + 1]) * inv);
-            st_shared_v4(stage + lane * 128 + ((c ^ (lane & 7)) << 4), v[0], v[1], v[2], v[3]);
-          }
+          for (int c = 0; c < 8; ++c)
+            st_shared_v4(stage + lane * 128 + ((c ^ (lane & 7)) << 4), v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA unit
           __syncwarp();
           if (lane == 0 && row0 < a.seq_q) {
