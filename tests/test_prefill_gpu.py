@@ -209,6 +209,24 @@ def test_adversarial_score_growth(kerns):
     check_close(run_masked(kerns, q, k, v, O.causal_mask(B, L)), want, "growing scores, dense mask")
 
 
+@pytest.mark.parametrize("D,dtype", [(128, torch.float16), (64, torch.float16), (128, torch.bfloat16)])
+def test_scores_that_jump_late_in_a_row(kerns, D, dtype):
+    """A few keys far into the sequence carry scores tens of units above everything before them - for some
+    rows only, positive for some and negative for others - in the first half, the second half and the last
+    chunk of their 128-key tiles: whatever reference the kernel keeps for a row has to move in the middle of
+    a tile, after part of the tile's P may already have been consumed."""
+    B, H, Hkv, L = 1, 4, 2, 768
+    q, k, v = seeded_qkv(55 + D, B, H, Hkv, L, L, D, dtype)
+    k = k.float()
+    for pos, gain in ((128 + 10, 40.0), (128 + 100, 25.0), (256 + 127, 60.0), (512 + 64, 30.0), (640 + 3, 80.0)):
+        k[:, :, pos] *= gain
+    k = k.to(dtype)
+    want = O.prefill_oracle(q, k, v, causal=True)
+    check_close(run_causal(kerns, q, k, v), want, "late jumps, causal entry", bf16=dtype == torch.bfloat16)
+    check_close(run_masked(kerns, q, k, v, O.causal_mask(B, L)), want, "late jumps, dense mask",
+                bf16=dtype == torch.bfloat16)
+
+
 def test_bf16_medium(kerns):
     q, k, v = seeded_qkv(7, 1, 8, 1, 1024, 1024, 128, torch.bfloat16)
     want = O.prefill_oracle(q, k, v, causal=True)
