@@ -136,6 +136,26 @@ def decode_oracle(q, k_cache, v_cache, lens) -> torch.Tensor:
     return F.scaled_dot_product_attention(qf, kf, vf, attn_mask=m, enable_gqa=(kf.shape[1] != H))
 
 
+def gather_pages(pages: torch.Tensor, block_table: torch.Tensor, lens) -> torch.Tensor:
+    """Contiguous cache [B, Hkv, max_pages * page, D] of a paged one: pool [n_pages, Hkv, page, D], block_table
+    [B, max_pages].  Only the table entries a sequence needs (below ceil(lens[b] / page)) are followed; the
+    rows of the other pages are zeros.  The reference's cache (src/minfer/core.py:105-127) has no pages: this
+    is the definition the paged kernels are held to."""
+    pages = pages.cpu()
+    n_pages, Hkv, page, D = pages.shape
+    B, max_pages = block_table.shape
+    out = torch.zeros(B, Hkv, max_pages * page, D, dtype=pages.dtype)
+    for b in range(B):
+        for j in range((int(lens[b]) + page - 1) // page):
+            out[b, :, j * page:(j + 1) * page] = pages[int(block_table[b, j])]
+    return out
+
+
+def decode_paged_oracle(q, k_pages, v_pages, block_table, lens) -> torch.Tensor:
+    """decode_oracle over the gathered cache."""
+    return decode_oracle(q, gather_pages(k_pages, block_table, lens), gather_pages(v_pages, block_table, lens), lens)
+
+
 def il_rope_reference(x: torch.Tensor, rotary_dim: int, start_pos: int, base_freq: float) -> torch.Tensor:
     """Interleaved RoPE restated from the reference (src/minfer/kernels/refs.py:12-28): fp32 angles
     (pos + start_pos) * base^(-2i/rot), complex rotation of pairs (2i, 2i+1); x is [B, L, H, D]."""

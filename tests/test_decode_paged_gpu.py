@@ -39,7 +39,7 @@ def test_paged_matches_oracle_and_contiguous_kernel(kerns, D, H, Hkv, page, dtyp
     kp, vp, table, kc, vc = make_paged(B, Hkv, D, page, lens, dtype, seed=5 + D + page)
     g = torch.Generator().manual_seed(99)
     q = torch.randn(B, H, 1, D, generator=g).to(dtype)
-    want = O.decode_oracle(q, kc, vc, lens)
+    want = O.decode_paged_oracle(q, kp, vp, table, lens)
     out_p = torch.full(q.shape, float("nan"), dtype=dtype, device="cuda")
     kerns.flash_attn_decode_paged(q.cuda(), kp.cuda(), vp.cuda(), table.cuda(), lens.cuda(), out_p)
     out_c = torch.full(q.shape, float("nan"), dtype=dtype, device="cuda")
