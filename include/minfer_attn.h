@@ -40,9 +40,10 @@ extern "C" {
  * two-tile warp-specialised one.  Same results within tolerance; kept for
  * cross-checking. */
 #define MINFER_ATTN_FLAG_SIMPLE_KERNEL 1
-/* Run the two-tile kernel with one work item per thread block instead of the
- * persistent form (one block per SM walking a list of items).  Dense-mask calls
- * always run this way.  Kept for cross-checking. */
+/* Run the earlier two-tile kernel with one work item per thread block (its own
+ * S region per query tile, one MMA-issuing warp) instead of the persistent form
+ * (one block per SM walking a list of items), for causal, unmasked and
+ * dense-mask calls alike.  Kept for cross-checking. */
 #define MINFER_ATTN_FLAG_ONE_ITEM_PER_CTA 2
 
 /* KV-cache formats (kv_format / cache_format fields) */

@@ -142,26 +142,39 @@ def test_dense_mask_without_workspace_matches(kerns):
     assert torch.equal(outs[0], outs[1])
 
 
-def test_simple_kernel_flag_agrees(kerns):
-    """MINFER_ATTN_FLAG_SIMPLE_KERNEL selects the single-tile kernel; both kernels meet the tolerance."""
+@pytest.mark.parametrize("D,H,Hkv", [(128, 4, 2), (64, 3, 1)])
+def test_kernel_selection_flags_agree(kerns, D, H, Hkv):
+    """flags = 0 (persistent kernel), MINFER_ATTN_FLAG_SIMPLE_KERNEL (single-tile kernel) and
+    MINFER_ATTN_FLAG_ONE_ITEM_PER_CTA (two-tile kernel, one work item per thread block) all meet the tolerance,
+    for the causal entry and for a dense mask with and without the tile-class workspace."""
     import ctypes
     from minfer.kernels.torch_ext import _lib
-    B, H, Hkv, L, D = 1, 4, 2, 640, 128
-    q, k, v = seeded_qkv(78, B, H, Hkv, L, L, D, torch.float16)
-    want = O.prefill_oracle(q, k, v, causal=True)
-    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
-    for flags in (0, 1):
-        out = torch.full((B, H, L, D), float("nan"), dtype=torch.float16, device="cuda")
-        p = _lib.PrefillParams()
-        p.q, p.k, p.v, p.out = qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr()
-        for i in range(3):
-            p.q_stride[i], p.kv_stride[i], p.out_stride[i] = qd.stride(i), kd.stride(i), out.stride(i)
-        p.batch, p.n_heads, p.n_kv_heads, p.seq_q, p.seq_k, p.head_dim = B, H, Hkv, L, L, D
-        p.dtype, p.causal, p.softmax_scale, p.flags = _lib.F16, 1, 0.0, flags
-        rc = _lib.lib.minfer_attn_prefill(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
-        assert rc == 0, _lib.strerror(rc)
-        torch.cuda.synchronize()
-        check_close(out, want, f"flags={flags}")
+    B, L = 2, 640
+    q, k, v = seeded_qkv(78 + D, B, H, Hkv, L, L, D, torch.float16)
+    mask = O.window_mask(B, L, 200).clone()
+    mask[:, :, 130:140] = False
+    wants = {"causal": O.prefill_oracle(q, k, v, causal=True), "mask": O.attention_f64(q, k, v, mask=mask)}
+    qd, kd, vd, md = q.cuda(), k.cuda(), v.cuda(), mask.cuda().contiguous()
+    need = _lib.lib.minfer_attn_prefill_workspace_bytes(B, L, L)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    for kind in ("causal", "mask"):
+        for flags in (0, 1, 2):
+            for use_ws in (False, True):
+                out = torch.full((B, H, L, D), float("nan"), dtype=torch.float16, device="cuda")
+                p = _lib.PrefillParams()
+                p.q, p.k, p.v, p.out = qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr()
+                if kind == "mask":
+                    p.mask = md.data_ptr()
+                for i in range(3):
+                    p.q_stride[i], p.kv_stride[i], p.out_stride[i] = qd.stride(i), kd.stride(i), out.stride(i)
+                p.batch, p.n_heads, p.n_kv_heads, p.seq_q, p.seq_k, p.head_dim = B, H, Hkv, L, L, D
+                p.dtype, p.causal, p.softmax_scale, p.flags = _lib.F16, int(kind == "causal"), 0.0, flags
+                if use_ws:
+                    p.workspace, p.workspace_bytes = ws.data_ptr(), need
+                rc = _lib.lib.minfer_attn_prefill(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                assert rc == 0, _lib.strerror(rc)
+                torch.cuda.synchronize()
+                check_close(out, wants[kind], f"{kind} flags={flags} workspace={use_ws}")
 
 
 @pytest.mark.parametrize("Lq,Lk,H,Hkv,D", [(200, 712, 4, 2, 128), (1, 300, 3, 3, 64), (384, 385, 8, 1, 128)])
