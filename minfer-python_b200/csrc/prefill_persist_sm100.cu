@@ -239,6 +239,10 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #endif
   constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
   constexpr int kRing = kMasked ? kMaskRing : kSchedRing;  // ring entries in use
+  // Bit c set: the exponentials of a tile's c-th 32-key chunk use the cubic on the FMA pipes.  At D = 64 the
+  // kernel is bound by the special-function unit alone (half the MMA work per exponential) and one chunk of four
+  // gains 6 %; a second chunk, or any at D = 128, loses.
+  constexpr int kPolyChunks = (D == 64) ? 2 : 0;
   constexpr int kKvEmpty = kKvFull + kStages;
   constexpr int kNumBars = kKvFull + 2 * kStages;
   constexpr uint32_t kTmemCols = 512;
@@ -799,9 +803,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             const float2 sp = make_float2(__uint_as_float(sr[c * 32 + 2 * e]), __uint_as_float(sr[c * 32 + 2 * e + 1]));
             const float2 x = __ffma2_rn(sp, sl2_2, nmb_2);
             float2 p;
-            // kPolyOf8 of every 8 pairs go through the FMA-pipe polynomial, the rest
-            // through the special-function unit
-            if ((e & 7) < kPolyOf8) {
+            // the chunks in kPolyChunks (and kPolyOf8 of every 8 pairs elsewhere) go through the FMA-pipe
+            // polynomial, the rest through the special-function unit
+            if (((kPolyChunks >> c) & 1) || (e & 7) < kPolyOf8) {
               p = ex2_poly2(x);
             } else {
               p.x = ex2_approx(x.x);
