@@ -242,7 +242,10 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   // Bit c set: the exponentials of a tile's c-th 32-key chunk use the cubic on the FMA pipes.  At D = 64 the
   // kernel is bound by the special-function unit alone (half the MMA work per exponential) and one chunk of four
   // gains 6 %; a second chunk, or any at D = 128, loses.
-  constexpr int kPolyChunks = (D == 64) ? 2 : 0;
+#ifndef MINFER_ATTN_POLY_CHUNKS_D128
+#define MINFER_ATTN_POLY_CHUNKS_D128 0
+#endif
+  constexpr int kPolyChunks = (D == 64) ? 2 : MINFER_ATTN_POLY_CHUNKS_D128;
   constexpr int kKvEmpty = kKvFull + kStages;
   constexpr int kNumBars = kKvFull + 2 * kStages;
   constexpr uint32_t kTmemCols = 512;
