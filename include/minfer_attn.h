@@ -29,26 +29,20 @@
 extern "C" {
 #endif
 
-#define MINFER_ATTN_ABI_VERSION 4
+#define MINFER_ATTN_ABI_VERSION 5
 
 /* element types of q/k/v/out */
 #define MINFER_ATTN_F16  0
 #define MINFER_ATTN_BF16 1
 
-/* MinferAttnPrefillParams.flags: run the single-tile kernel (one 128-row query
- * tile per thread block, no overlap of softmax and MMA) instead of the
- * two-tile warp-specialised one.  Same results within tolerance; kept for
- * cross-checking. */
-#define MINFER_ATTN_FLAG_SIMPLE_KERNEL 1
-/* Run the earlier two-tile kernel with one work item per thread block (its own
- * S region per query tile, one MMA-issuing warp) instead of the persistent form
- * (one block per SM walking a list of items), for causal, unmasked and
- * dense-mask calls alike.  Kept for cross-checking. */
-#define MINFER_ATTN_FLAG_ONE_ITEM_PER_CTA 2
-
 /* KV-cache formats (kv_format / cache_format fields) */
 #define MINFER_ATTN_KV_16BIT 0  /* the same 16-bit type as q                                    */
 #define MINFER_ATTN_KV_Q8_0  1  /* GGML Q8_0 blocks: 32 int8 + one fp16 scale = 34 bytes        */
+
+/* status[0] values a kernel may leave in a caller-provided status word (device int32[4]) */
+#define MINFER_ATTN_STATUS_WAIT_TIMEOUT 100  /* {code, blockIdx.x, blockIdx.y, wait site}                       */
+#define MINFER_ATTN_STATUS_BAD_PAGE     101  /* {code, sequence, table index, entry}: entry outside [0, n_pages) */
+#define MINFER_ATTN_STATUS_BAD_POSITION 102  /* {code, sequence, position, max_len}: row outside the cache       */
 
 /* error codes */
 #define MINFER_ATTN_OK            0
@@ -81,8 +75,10 @@ extern "C" {
  * refs.py:55).  head_dim is 64 or 128.
  *
  * status: optional device int32[4].  A kernel that gives up a bounded wait
- * writes {code, blockIdx.x, blockIdx.y, site} there; it is never written on
- * success.  The caller zeroes it and reads it after synchronising.
+ * writes {MINFER_ATTN_STATUS_WAIT_TIMEOUT, blockIdx.x, blockIdx.y, site} there;
+ * it is never written on success.  The caller zeroes it and reads it after
+ * synchronising.  (The decode and RoPE structs carry the same kind of word for
+ * bad block-table entries and out-of-range positions, see there.)
  */
 typedef struct MinferAttnPrefillParams {
   const void*    q;
@@ -103,9 +99,12 @@ typedef struct MinferAttnPrefillParams {
   int32_t dtype;          /* MINFER_ATTN_F16 / MINFER_ATTN_BF16 */
   int32_t causal;
   float   softmax_scale;
-  int32_t flags;          /* 0, or MINFER_ATTN_FLAG_* */
+  int32_t flags;          /* reserved, must be 0 */
   void*   workspace;      /* optional device scratch for dense masks, see below */
   size_t  workspace_bytes;
+  int32_t max_ctas;       /* 0: one thread block per SM; n > 0: at most n thread blocks (leaves SMs free for
+                             kernels of other streams, e.g. a collective that overlaps this call) */
+  int32_t reserved;       /* must be 0 */
 } MinferAttnPrefillParams;
 
 int minfer_attn_prefill(const MinferAttnPrefillParams* params, void* stream);
@@ -149,7 +148,8 @@ size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t
  * reference's block_q8_0, csrc/common/types.hpp:141-146): a cache row is
  * head_dim/32 blocks of 34 bytes, rows of one (batch, head) are contiguous,
  * kv_stride[0] and kv_stride[1] are then in BYTES (multiples of 16) and
- * kv_stride[2] is ignored; max_len must be even.  Every cached value is used as
+ * kv_stride[2] is ignored; max_len must be even (a multiple of 4 for head_dim 64),
+ * so that the rows of one (batch, head) end on a 16-byte boundary.  Every cached value is used as
  * (16-bit type)(q * d), the reference's dequant_row_q8_0 (csrc/quants/impl.cpp:
  * 1153-1166), so the result equals the 16-bit path run on the dequantised cache.
  *
@@ -185,6 +185,10 @@ typedef struct MinferAttnDecodeParams {
   const int32_t* block_table;  /* NULL: contiguous cache; else device int32[batch, table_stride] of page indices */
   int32_t page_size;      /* keys per page (multiple of 16); ignored without a block table */
   int32_t table_stride;   /* entries per sequence in block_table */
+  int32_t n_pages;        /* pages in the pools (required with a block table): an entry outside [0, n_pages) is
+                             never dereferenced - the kernel reads page 0 instead and reports it through status */
+  int32_t flags;          /* reserved, must be 0 */
+  int32_t* status;        /* optional device int32[4], see MINFER_ATTN_STATUS_BAD_PAGE; written only on error */
 } MinferAttnDecodeParams;
 
 int minfer_attn_decode(const MinferAttnDecodeParams* params, void* stream);
@@ -210,8 +214,14 @@ int32_t minfer_attn_decode_default_chunk(int32_t batch, int32_t n_kv_heads,
  *   - A shape whose partials need more than that is refused with
  *     MINFER_ATTN_ETOOLARGE and nothing is launched (the need is
  *     minfer_attn_decode_workspace_bytes() for the same arguments).
- *   - The first call on a device looks up the array's device address; make
- *     that first call before any stream capture begins on that device.
+ *   - The first call on a device looks up the array's device address, and with
+ *     the CUDA runtime's lazy module loading that first call (not loading the
+ *     library) is also when the device reserves the array's bytes.  Make that
+ *     first call - a small warm-up shape will do - before any stream capture
+ *     begins on that device and BEFORE the process hands the rest of the
+ *     device's memory to its own pool; a pool filled first leaves no room for
+ *     the array and the call then fails with MINFER_ATTN_ECUDA
+ *     (minfer_attn_last_cuda_error() names the cause).
  *   - All calls on a device share the one array.  Nothing in it has to start
  *     at zero (every partial that is read was written earlier in the same
  *     call), but two calls whose kernels overlap on the GPU race on it: issue
@@ -241,7 +251,10 @@ int minfer_attn_decode_static(const MinferAttnDecodeParams* params, void* stream
  * innermost stride 1, multiples of 8; pointers 16-byte aligned.  rotary_dim is
  * a multiple of 8 (16 for the neox style) and at most head_dim; head_dim is a
  * multiple of 8.  style: 0 = interleaved pairs, 1 = neox (two halves).
- * The caller guarantees start[b] + seq <= max_len.
+ * A position start[b] + l outside [0, max_len) is not written to the caches
+ * (q is still rotated) and is reported through `status`; the scalar start_pos is
+ * checked on the host.  The reference's kernels accept any even rotary_dim; this
+ * one moves 16-byte chunks and therefore wants the granularity stated above.
  *
  * cache_format == MINFER_ATTN_KV_Q8_0: the caches hold Q8_0 blocks (layout as for
  * minfer_attn_decode; cache_stride[0..1] in bytes, [2] ignored): the row the
@@ -274,6 +287,11 @@ typedef struct MinferRopeParams {
   const int32_t* block_table;  /* NULL, or the paged cache's int32[batch, table_stride] (see MinferAttnDecodeParams): */
   int32_t page_size;      /*   row start[b] + l goes to page block_table[b][pos / page_size], row pos % page_size; */
   int32_t table_stride;   /*   cache_stride[0] is then the stride between pages and page_size may be any value > 0 */
+  int32_t n_pages;        /* pages in the pools (required with a block table); a table entry outside [0, n_pages)
+                             is not followed: that row is not written and status reports it */
+  int32_t flags;          /* reserved, must be 0 */
+  int32_t* status;        /* optional device int32[4]: MINFER_ATTN_STATUS_BAD_PAGE / _BAD_POSITION; written only
+                             on error */
 } MinferRopeParams;
 
 int minfer_attn_rope_append(const MinferRopeParams* params, void* stream);

@@ -2,8 +2,8 @@
 
 Replaces the reference's setup.py CUDAExtension build
 (setup.py:19-86 of dsuarez01/minfer-python, which targets compute_89 and asserts
-a GPU at build time): one `nvcc -shared` over the three translation units, one
-target architecture, no GPU needed to build.
+a GPU at build time): the translation units in SOURCES compiled in parallel and
+linked by one `nvcc -shared`, one target architecture, no GPU needed to build.
 
 Usage:  python build.py [--force] [--verbose]
 """
@@ -20,7 +20,8 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OUT_DIR = os.path.join(HERE, "minfer", "kernels", "torch_ext")
 LIB_NAME = "libminfer_attn.so"
-SOURCES = ["attn_api.cu", "prefill_sm100.cu", "prefill_ws_sm100.cu", "prefill_persist_sm100.cu", "mask_classify.cu", "decode_sm100.cu", "decode_static_sm100.cu", "rope_append_sm100.cu"]
+SOURCES = ["attn_api.cu", "prefill_persist_sm100.cu", "mask_classify.cu", "decode_sm100.cu", "decode_static_sm100.cu",
+           "rope_append_sm100.cu"]
 HEADERS = ["attn_internal.h", "ptx.cuh"]
 
 NVCC_FLAGS = [

@@ -7,6 +7,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstring>
 #include <mutex>
 
 namespace minfer_attn {
@@ -45,8 +46,8 @@ int check_device() {
 // strides (s_b, s_h, s_r, 1).  The three outer dimensions are ordered by
 // ascending stride; pos[] receives the coordinate slot (1..3) of batch, head
 // and row.  Box = 64 elements x box_rows rows, 128-byte swizzle, zero fill.
-int make_tensor_map(CUtensorMap* tm, const void* base, bool bf16, int head_dim, int64_t batch, int64_t heads,
-                    int64_t rows, const int64_t stride[3], int32_t pos[3], int box_rows = 128) {
+int encode_tensor_map(CUtensorMap* tm, const void* base, bool bf16, int head_dim, int64_t batch, int64_t heads,
+                      int64_t rows, const int64_t stride[3], int32_t pos[3], int box_rows) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return MINFER_ATTN_ECUDA;
   struct Dim {
@@ -76,12 +77,50 @@ int make_tensor_map(CUtensorMap* tm, const void* base, bool bf16, int head_dim, 
   return r == CUDA_SUCCESS ? MINFER_ATTN_OK : MINFER_ATTN_EINVAL;
 }
 
-thread_local cudaError_t g_last_cuda_error = cudaSuccess;
+// A tensor map is a pure function of (base, type, extents, strides, box), and a decode loop or a
+// benchmark calls with the same tensors over and over: keep the encoded maps in a small per-thread,
+// direct-mapped table so that a repeated call costs a hash and a compare instead of four driver calls.
+struct MapKey {
+  int64_t base, batch, heads, rows, stride[3], misc;  // misc: head_dim | box_rows << 16 | bf16 << 32
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+  int32_t pos[3];
+  bool valid;
+};
+constexpr int kMapCacheSize = 64;
 
-int cuda_result(cudaError_t e) {
-  g_last_cuda_error = e;
-  return e == cudaSuccess ? MINFER_ATTN_OK : MINFER_ATTN_ECUDA;
+int make_tensor_map(CUtensorMap* tm, const void* base, bool bf16, int head_dim, int64_t batch, int64_t heads,
+                    int64_t rows, const int64_t stride[3], int32_t pos[3], int box_rows = 128) {
+  alignas(64) static thread_local MapEntry cache[kMapCacheSize] = {};
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.base = static_cast<int64_t>(reinterpret_cast<uintptr_t>(base));
+  key.batch = batch;
+  key.heads = heads;
+  key.rows = rows;
+  for (int i = 0; i < 3; ++i) key.stride[i] = stride[i];
+  key.misc = static_cast<int64_t>(head_dim) | (static_cast<int64_t>(box_rows) << 16) | (static_cast<int64_t>(bf16) << 32);
+  uint64_t h = 1469598103934665603ull;
+  const uint64_t* w = reinterpret_cast<const uint64_t*>(&key);
+  for (size_t i = 0; i < sizeof(key) / 8; ++i) h = (h ^ w[i]) * 1099511628211ull;
+  MapEntry& e = cache[(h >> 20) % kMapCacheSize];
+  if (e.valid && std::memcmp(&e.key, &key, sizeof(key)) == 0) {
+    *tm = e.map;
+    for (int i = 0; i < 3; ++i) pos[i] = e.pos[i];
+    return MINFER_ATTN_OK;
+  }
+  const int rc = encode_tensor_map(tm, base, bf16, head_dim, batch, heads, rows, stride, pos, box_rows);
+  if (rc != MINFER_ATTN_OK) return rc;
+  e.key = key;
+  e.map = *tm;
+  for (int i = 0; i < 3; ++i) e.pos[i] = pos[i];
+  e.valid = true;
+  return MINFER_ATTN_OK;
 }
+
+thread_local cudaError_t g_last_cuda_error = cudaSuccess;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -100,6 +139,13 @@ int32_t default_chunk(int32_t batch, int32_t n_kv_heads, int32_t max_len) {
 }
 
 }  // namespace
+
+int cuda_result(cudaError_t e) {
+  g_last_cuda_error = e;
+  if (e != cudaSuccess) (void)cudaGetLastError();  // clear the runtime's (non-sticky) error state
+  return e == cudaSuccess ? MINFER_ATTN_OK : MINFER_ATTN_ECUDA;
+}
+
 }  // namespace minfer_attn
 
 using namespace minfer_attn;
@@ -137,6 +183,8 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
     return MINFER_ATTN_EINVAL;
   if (!(p->softmax_scale >= 0.f)) return MINFER_ATTN_EINVAL;
   if (p->batch > 65535 || p->n_heads > 65535) return MINFER_ATTN_EUNSUPPORTED;
+  if (p->flags != 0 || p->reserved != 0) return MINFER_ATTN_EUNSUPPORTED;
+  if (p->max_ctas < 0) return MINFER_ATTN_EINVAL;
   // the masked kernel's tile list holds 1024 key tiles
   if (!p->causal && p->mask != nullptr && p->seq_k > 128 * 1024) return MINFER_ATTN_EUNSUPPORTED;
   int rc = check_device();
@@ -168,7 +216,7 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
     a.counter = static_cast<int*>(p->workspace);
   if (a.mask != nullptr) {
     const size_t need = minfer_attn_prefill_workspace_bytes(p->batch, p->seq_q, p->seq_k);
-    if (a.counter != nullptr && p->workspace_bytes >= need && !(p->flags & MINFER_ATTN_FLAG_SIMPLE_KERNEL)) {
+    if (a.counter != nullptr && p->workspace_bytes >= need) {
       uint8_t* cls = static_cast<uint8_t*>(p->workspace) + 16;
       cudaError_t ce = launch_mask_classify(a.mask, cls, p->batch, p->seq_q, p->seq_k, static_cast<cudaStream_t>(stream));
       if (ce != cudaSuccess) return cuda_result(ce);
@@ -189,13 +237,8 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
   a.scale_log2 = scale * 1.4426950408889634f;
 
   a.pair_heads = (a.group % 2 == 0) ? 1 : 0;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e;
-  if (p->flags & MINFER_ATTN_FLAG_SIMPLE_KERNEL) e = launch_prefill(tq, tk, tv, a, p->head_dim, bf16, st);
-  else if (p->flags & MINFER_ATTN_FLAG_ONE_ITEM_PER_CTA)
-    e = launch_prefill_ws(tq, tk, tv, a, p->head_dim, bf16, st);
-  else e = launch_prefill_persist(tq, tk, tv, to, a, p->head_dim, bf16, st);
-  return cuda_result(e);
+  a.max_ctas = p->max_ctas;
+  return cuda_result(launch_prefill_persist(tq, tk, tv, to, a, p->head_dim, bf16, static_cast<cudaStream_t>(stream)));
 }
 
 size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t seq_k) {
@@ -231,7 +274,8 @@ int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {
     if (p->max_len <= 0) return MINFER_ATTN_EINVAL;
     if (p->start == nullptr && (p->start_pos < 0 || p->start_pos + p->seq > p->max_len)) return MINFER_ATTN_EINVAL;
     if (p->block_table != nullptr) {
-      if (p->page_size <= 0 || p->table_stride <= 0 || (reinterpret_cast<uintptr_t>(p->block_table) & 3) != 0)
+      if (p->page_size <= 0 || p->table_stride <= 0 || p->n_pages <= 0 ||
+          (reinterpret_cast<uintptr_t>(p->block_table) & 3) != 0)
         return MINFER_ATTN_EINVAL;
       if (static_cast<int64_t>(p->page_size) * p->table_stride < p->max_len) return MINFER_ATTN_EINVAL;
     }
@@ -239,6 +283,8 @@ int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {
     return MINFER_ATTN_EINVAL;
   }
   if (p->start == nullptr && p->start_pos < 0) return MINFER_ATTN_EINVAL;
+  if (p->flags != 0) return MINFER_ATTN_EUNSUPPORTED;
+  if (p->status != nullptr && (reinterpret_cast<uintptr_t>(p->status) & 3) != 0) return MINFER_ATTN_EINVAL;
   int rc = check_device();
   if (rc != MINFER_ATTN_OK) return rc;
   RopeArgs a{};
@@ -260,6 +306,9 @@ int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {
   a.head_dim = p->head_dim;
   a.rotary_dim = p->rotary_dim;
   a.start_pos = p->start_pos;
+  a.max_len = p->max_len;
+  a.n_pages = p->block_table != nullptr ? p->n_pages : 0;
+  a.status = p->status;
   a.freq_base = p->freq_base;
   a.cache_q8 = cq8 ? 1 : 0;
   a.block_table = p->block_table;
@@ -300,17 +349,21 @@ int minfer_attn_decode(const MinferAttnDecodeParams* p, void* stream) {
   if (q8) {
     if (p->kv_stride[0] < 0 || p->kv_stride[1] < 0 || p->kv_stride[0] % 16 != 0 || p->kv_stride[1] % 16 != 0)
       return MINFER_ATTN_EINVAL;
-    if (p->max_len % 2 != 0) return MINFER_ATTN_EINVAL;
+    // the rows of one (batch, head) must end on a 16-byte boundary (rows are 136 / 68 bytes)
+    if (p->max_len % (p->head_dim == 64 ? 4 : 2) != 0) return MINFER_ATTN_EINVAL;
   } else if (!strides_ok(p->kv_stride, 3)) {
     return MINFER_ATTN_EINVAL;
   }
   if (!(p->softmax_scale >= 0.f)) return MINFER_ATTN_EINVAL;
   if (p->batch > 65535 || p->n_kv_heads > 65535) return MINFER_ATTN_EUNSUPPORTED;
   if (p->block_table != nullptr) {
-    if (p->page_size <= 0 || p->page_size % 16 != 0 || p->table_stride <= 0) return MINFER_ATTN_EINVAL;
+    if (p->page_size <= 0 || p->page_size % 16 != 0 || p->table_stride <= 0 || p->n_pages <= 0)
+      return MINFER_ATTN_EINVAL;
     if (static_cast<int64_t>(p->table_stride) * p->page_size < p->max_len) return MINFER_ATTN_EINVAL;
     if ((reinterpret_cast<uintptr_t>(p->block_table) & 3) != 0) return MINFER_ATTN_EINVAL;
   }
+  if (p->flags != 0) return MINFER_ATTN_EUNSUPPORTED;
+  if (p->status != nullptr && (reinterpret_cast<uintptr_t>(p->status) & 3) != 0) return MINFER_ATTN_EINVAL;
   int32_t chunk = p->chunk;
   if (chunk == 0) chunk = default_chunk(p->batch, p->n_kv_heads, p->max_len);
   if (chunk < 64 || chunk % 64 != 0) return MINFER_ATTN_EINVAL;
@@ -344,6 +397,8 @@ int minfer_attn_decode(const MinferAttnDecodeParams* p, void* stream) {
   a.block_table = p->block_table;
   a.page_size = p->block_table != nullptr ? p->page_size : 0;
   a.table_stride = p->block_table != nullptr ? p->table_stride : 0;
+  a.n_pages = p->block_table != nullptr ? p->n_pages : 0;
+  a.status = p->status;
 
   cudaError_t e = launch_decode(a, p->head_dim, p->dtype == MINFER_ATTN_BF16, q8, static_cast<cudaStream_t>(stream));
   return cuda_result(e);

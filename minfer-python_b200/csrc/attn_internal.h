@@ -8,8 +8,14 @@
 
 namespace minfer_attn {
 
-// value a kernel writes to status[0] when a bounded wait runs out
-constexpr int32_t kStatusWaitTimeout = 100;
+// values a kernel writes to status[0] (MINFER_ATTN_STATUS_* of the public header)
+constexpr int32_t kStatusWaitTimeout = 100;  // a bounded wait ran out
+constexpr int32_t kStatusBadPage = 101;      // a block-table entry outside [0, n_pages)
+constexpr int32_t kStatusBadPosition = 102;  // a cache row outside [0, max_len)
+
+// Records `e` as the calling thread's latest CUDA result (what minfer_attn_last_cuda_error() reports)
+// and maps it to MINFER_ATTN_OK / MINFER_ATTN_ECUDA.
+int cuda_result(cudaError_t e);
 
 // Kernel-side view of a prefill call (tensor maps travel separately).
 struct PrefillArgs {
@@ -23,7 +29,8 @@ struct PrefillArgs {
   int32_t group;          // query heads per kv head
   int32_t causal;
   int32_t mask_vec;       // mask rows may be read with 16-byte loads
-  int32_t pair_heads;     // two-tile kernel: slots are two heads of one kv head (else two row tiles)
+  int32_t pair_heads;     // slots are two heads of one kv head (else two row tiles of one head)
+  int32_t max_ctas;       // upper bound on the grid (0: one CTA per SM)
   int32_t items_x, items_y;  // persistent kernel: work-item grid (query tile [pairs], head [pairs]); set by its launcher
   int32_t order_by_kv_set;   // persistent kernel, dynamic claiming: item order (see its launcher)
   float scale_log2;       // softmax scale * log2(e)
@@ -34,13 +41,8 @@ struct PrefillArgs {
   int32_t out_pos[3];  // coordinate slots of the output tensor map (persistent kernel only)
 };
 
-size_t prefill_smem_bytes(int head_dim);
-cudaError_t launch_prefill_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                              const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream);
 cudaError_t launch_prefill_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                                    const CUtensorMap& to, const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream);
-cudaError_t launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillArgs& a,
-                           int head_dim, bool bf16, cudaStream_t stream);
 
 // Classifies every 128 x 128 tile of a dense [batch, 1, seq_q, seq_k] byte mask: 0 = no byte set,
 // 1 = every in-range byte set, 2 = mixed.  cls is [batch, ceil(seq_q/128), ceil(seq_k/128)].
@@ -59,6 +61,9 @@ struct RopeArgs {
   int64_t kv_stride[3];     // batch, token, head
   int64_t cache_stride[3];  // batch, head, row
   int32_t batch, seq, n_heads, n_kv_heads, head_dim, rotary_dim, start_pos;
+  int32_t max_len;          // rows per (batch, head) of the caches: positions outside [0, max_len) are not written
+  int32_t n_pages;          // paged cache: valid table entries are [0, n_pages)
+  int32_t* status;          // optional device int32[4] for kStatusBadPage / kStatusBadPosition
   int32_t cache_q8;         // caches hold GGML Q8_0 blocks; cache_stride then in bytes (batch, head), rows contiguous
   float freq_base;
   const int32_t* block_table;  // paged cache: [batch, table_stride] page indices; cache_stride[0] is then per page
@@ -85,6 +90,8 @@ struct DecodeArgs {
   float scale_log2;
   const int32_t* block_table;  // paged cache: [batch, table_stride] page indices; kv_stride[0] is then per page
   int32_t page_size, table_stride;
+  int32_t n_pages;             // paged cache: valid table entries are [0, n_pages)
+  int32_t* status;             // optional device int32[4] for kStatusBadPage
 };
 
 cudaError_t launch_decode(const DecodeArgs& a, int head_dim, bool bf16, bool q8, cudaStream_t stream);

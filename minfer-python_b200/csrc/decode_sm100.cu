@@ -137,7 +137,17 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
     const size_t row_bytes = Q8 ? static_cast<size_t>((D / 32) * 34) : 2 * static_cast<size_t>(a.kv_stride[2]);
     const size_t head_off = kUnit * static_cast<size_t>(kvh) * a.kv_stride[1];
     if constexpr (Paged) {
-      const int page = __ldg(a.block_table + static_cast<size_t>(b) * a.table_stride + key0 / a.page_size);
+      const int slot = key0 / a.page_size;
+      int page = __ldg(a.block_table + static_cast<size_t>(b) * a.table_stride + slot);
+      if (static_cast<unsigned>(page) >= static_cast<unsigned>(a.n_pages)) {
+        // never follow an entry that points outside the pools: report it and read page 0 instead
+        if (lane == 0 && a.status != nullptr && atomicCAS(a.status, 0, kStatusBadPage) == 0) {
+          a.status[1] = b;
+          a.status[2] = slot;
+          a.status[3] = page;
+        }
+        page = 0;
+      }
       return kUnit * static_cast<size_t>(page) * a.kv_stride[0] + head_off + static_cast<size_t>(key0 % a.page_size) * row_bytes;
     }
     return kUnit * static_cast<size_t>(b) * a.kv_stride[0] + head_off + static_cast<size_t>(key0) * row_bytes;

@@ -3,11 +3,13 @@
 // minfer_attn_decode() needs a caller-provided workspace for its split-KV
 // partials.  Some callers cannot provide one: a serving process that handed
 // all of its device memory to a KV-cache pool at start-up (any later
-// allocation fails), or a latency-critical decode loop that cannot afford the
+// allocation fails; such a process makes its first call here BEFORE it fills
+// the pool, see scratch_on_current_device), or a latency-critical decode loop that cannot afford the
 // device-wide synchronisation an allocation may imply.  For them this file
 // offers the same kernels with the partials kept in a fixed array that is part
 // of the library image.  It has no counterpart in the reference.
 #include "../../include/minfer_attn.h"
+#include "attn_internal.h"
 
 #include <cuda_runtime.h>
 
@@ -24,15 +26,21 @@ void* g_scratch_addr[kMaxDevices] = {};
 std::mutex g_scratch_mu;
 
 // In host code `g_decode_scratch` is only a handle for the runtime, not a
-// device address; the address on the current device has to be looked up.
+// device address; the address on the current device has to be looked up.  With
+// lazy module loading this lookup is also the moment the device reserves the
+// array, so it can fail for lack of memory: the result goes through the same
+// last-error record as every other entry point.
 int scratch_on_current_device(void** out) {
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return MINFER_ATTN_ECUDA;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return minfer_attn::cuda_result(e);
   if (dev < 0 || dev >= kMaxDevices) return MINFER_ATTN_EUNSUPPORTED;
   std::lock_guard<std::mutex> lock(g_scratch_mu);
   if (g_scratch_addr[dev] == nullptr) {
     void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_decode_scratch) != cudaSuccess || ptr == nullptr) return MINFER_ATTN_ECUDA;
+    e = cudaGetSymbolAddress(&ptr, g_decode_scratch);
+    if (e != cudaSuccess) return minfer_attn::cuda_result(e);
+    if (ptr == nullptr) return minfer_attn::cuda_result(cudaErrorInvalidSymbol);
     g_scratch_addr[dev] = ptr;
   }
   *out = g_scratch_addr[dev];

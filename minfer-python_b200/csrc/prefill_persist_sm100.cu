@@ -1,9 +1,8 @@
-// Persistent form of the two-tile prefill kernel: causal, unmasked and dense-mask calls.
+// Persistent two-tile prefill kernel: causal, unmasked and dense-mask calls.
 //
-// Same roles, tensor-memory layout and MMA issue order as prefill_ws_sm100.cu
-// (the one-item-per-CTA form kept for cross-checking), but one CTA per SM walks a list of
-// work items instead of exiting after one.  What that buys: tensor memory and the
-// barriers are set up once; the TMA warp already streams the next item's Q/K/V
+// A work item is two 128-row query tiles ("slots") that share every K/V tile.  One CTA
+// per SM walks a list of work items instead of exiting after one.  What that buys: tensor
+// memory and the barriers are set up once; the TMA warp already streams the next item's Q/K/V
 // while the softmax warps write the previous item's output; and the MMA warp
 // starts the next item's first score tiles as soon as its operands have landed,
 // so the ~3k-cycle prologue and most of the epilogue of an item disappear from
@@ -32,7 +31,7 @@
 //   o_free[s]   softmax -> MMA  the epilogue has copied O_s out of tensor memory
 // The K/V ring simply continues across items.
 //
-// Three more differences from the one-item kernel.  (1) One S region for both slots
+// Roles and tensor memory.  (1) One S region for both slots
 // (tensor memory: S [0,128), P0 [128,192), P1 [192,256), O0, O1): warp 8 issues every
 // score MMA, the two slots taking the region in turn, and the next one is issued as
 // soon as the softmax warps of the previous one hold their scores in registers
@@ -96,9 +95,14 @@ constexpr int kKvFull = 30;  // [kStages], then kKvEmpty [kStages]
 constexpr int kMaxTiles = 1024;  // key tiles a masked call may have (seq_k <= 131072)
 constexpr int kMaskRing = 3;     // ring entries used by dense-mask calls (their bit planes must fit beside four K/V stages)
 
-// Optional accounting for tuning (compiled in only with -DMINFER_ATTN_TRACE): thread 0 of every CTA
-// (slot 0, row 0) sums where its clocks went and writes 8 words behind the 16 status words.
+// Optional accounting for tuning (compiled in only with -DMINFER_ATTN_TRACE): one thread per slot of every
+// CTA sums where its clocks went, and CTA 0 records a timeline of its first item, into a buffer of the
+// library's own (g_trace) that minfer_attn_debug_read_trace() copies to the host.  The product build
+// has neither.
 #ifdef MINFER_ATTN_TRACE
+constexpr int kTraceCtas = 160;
+constexpr int kTraceWords = kTraceCtas * 2 * 12 + 7 * 64 * 12;
+__device__ long long g_trace[kTraceWords];
 #define P_ACC(stmt) do { if (acc_on) { stmt; } } while (0)
 // timeline of CTA 0's first item: role r (0/1 softmax slot, 2 S issuer, 3 PV issuer), tile jj, event e
 #define P_TL(r, jj, e) do { if (tl_on && k == 0 && (jj) < 64) tl_buf[((r) * 64 + (jj)) * 12 + (e)] = clock64(); } while (0)
@@ -272,9 +276,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   // items (and, for dense masks, their tile lists) reach the consumer roles through the ring
   const bool use_ring = dynamic || kMasked;
 #ifdef MINFER_ATTN_TRACE
-  const bool tl_on = a.status != nullptr && blockIdx.x == 0 && (tid & 127) == 0;  // threads 0, 128, 256 (S issuer); PV issuer: 320
-  const bool tl_on2 = a.status != nullptr && blockIdx.x == 0 && tid == 320;
-  long long* tl_buf = reinterpret_cast<long long*>(a.status + 16) + 148 * 2 * 12;
+  const bool tl_on = blockIdx.x == 0 && (tid & 127) == 0;  // threads 0, 128, 256 (S issuer); PV issuer: 320
+  const bool tl_on2 = blockIdx.x == 0 && tid == 320;
+  long long* tl_buf = g_trace + kTraceCtas * 2 * 12;
 #endif
   // k-th item of this CTA as seen by a consumer role (MMA, softmax): from the ring, else by the static
   // rule; -1 = no more
@@ -663,7 +667,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     bool ok = true;
     uint32_t jt = 0;  // key tiles this slot has processed over the CTA's lifetime
 #ifdef MINFER_ATTN_TRACE
-    const bool acc_on = a.status != nullptr && (tid & 127) == 0;
+    const bool acc_on = (tid & 127) == 0 && blockIdx.x < kTraceCtas;
     long long acc_t0 = clock64(), acc_c = 0, acc_first = 0, acc_wait = 0, acc_epi = 0, acc_sched = 0, acc_items = 0, acc_ld = 0, acc_max = 0, acc_exp = 0, acc_resc = 0, acc_c2 = 0, acc_ew = 0, acc_el = 0;
 #endif
 
@@ -837,7 +841,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       if (!(ok = mbar_wait(&bars[kODone + s], (jt - 1) & 1u, abort_flag))) { report_p(a.status, 42); break; }
       P_ACC(acc_c2 = clock64(); acc_ew += acc_c2 - acc_c);
       tc_fence_after();
-      const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
+      // a row that never saw a visible key (m_ref still -inf) is zeros, whatever the exponentials of
+      // its masked scores summed to (the FMA-pipe cubic returns a tiny positive value for -inf)
+      const float inv = (m_ref != -INFINITY && l_run > 0.f) ? 1.f / l_run : 0.f;
       // A thread owns one row of O, but a row-per-thread store would touch 32 cache lines per
       // instruction and hold the warp behind the SM's store path.  Instead each warp packs 64 columns of
       // its 32 rows into its own 4 KB of shared memory (16-byte chunks XOR-swizzled by row, the layout of
@@ -886,7 +892,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     if (lane == 0) bulk_wait_all();  // the staging buffers stay allocated until the last box has left
 #ifdef MINFER_ATTN_TRACE
     if (acc_on) {
-      long long* w = reinterpret_cast<long long*>(a.status + 16) + (blockIdx.x * 2 + s) * 12;
+      long long* w = g_trace + (blockIdx.x * 2 + s) * 12;
       w[0] = clock64() - acc_t0; w[1] = acc_first; w[2] = acc_wait; w[3] = acc_epi;
       w[4] = acc_sched; w[5] = acc_items; w[6] = jt; w[7] = acc_ld; w[8] = acc_max; w[9] = acc_exp; w[10] = acc_resc; w[11] = (acc_ew << 32) | acc_el;
     }
@@ -930,7 +936,9 @@ cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, con
   a.items_y = a.pair_heads ? a.n_heads / 2 : a.n_heads;
   const long long n_items = static_cast<long long>(a.items_x) * a.items_y * a.batch;
   if (n_items > 0x7FFFFFFF) return cudaErrorInvalidValue;
-  const int grid = static_cast<int>(n_items < sm_count[dev] ? n_items : sm_count[dev]);
+  int ctas = sm_count[dev];
+  if (a.max_ctas > 0 && a.max_ctas < ctas) ctas = a.max_ctas;
+  const int grid = static_cast<int>(n_items < ctas ? n_items : ctas);
   // Order of the dynamically claimed items: globally longest-first while all K/V of the call fit
   // comfortably in the 126 MB L2; grouped by (batch, kv head) beyond that, so that the CTAs running
   // at one time share a few K/V sets instead of sweeping all of them.
@@ -945,6 +953,14 @@ cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, con
 }
 
 }  // namespace
+
+#ifdef MINFER_ATTN_TRACE
+// tuning builds only: copies the accounting buffer of the latest launches to the host
+extern "C" int minfer_attn_debug_read_trace(void* dst, size_t bytes) {
+  if (bytes > sizeof(long long) * kTraceWords) bytes = sizeof(long long) * kTraceWords;
+  return cudaMemcpyFromSymbol(dst, g_trace, bytes) == cudaSuccess ? 0 : 3;
+}
+#endif
 
 cudaError_t launch_prefill_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                                    const CUtensorMap& to, const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream) {

@@ -130,10 +130,33 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
   // contiguous [batch][head][row] caches, or a pool of pages reached through the block table
   size_t cb = static_cast<size_t>(b);
   int crow = pos;
-  if (a.block_table != nullptr) {
-    cb = static_cast<size_t>(a.block_table[static_cast<size_t>(b) * a.table_stride + pos / a.page_size]);
+  // A position outside the cache, or a table entry outside the pools, is never written: the row is
+  // dropped (q is still rotated) and the first such event is reported through the status word.  The
+  // threads of one token decide alike, so the shuffles of the Q8_0 path stay among live threads.
+  bool cache_ok = a.k_cache != nullptr;
+  if (cache_ok && (pos < 0 || pos >= a.max_len)) {
+    cache_ok = false;
+    if (a.status != nullptr && atomicCAS(a.status, 0, kStatusBadPosition) == 0) {
+      a.status[1] = b;
+      a.status[2] = pos;
+      a.status[3] = a.max_len;
+    }
+  }
+  if (cache_ok && a.block_table != nullptr) {
+    const int slot = pos / a.page_size;
+    const int page = a.block_table[static_cast<size_t>(b) * a.table_stride + slot];
+    if (static_cast<unsigned>(page) >= static_cast<unsigned>(a.n_pages)) {
+      cache_ok = false;
+      if (a.status != nullptr && atomicCAS(a.status, 0, kStatusBadPage) == 0) {
+        a.status[1] = b;
+        a.status[2] = slot;
+        a.status[3] = page;
+      }
+    }
+    cb = static_cast<size_t>(page);
     crow = pos % a.page_size;
   }
+  const bool to_cache = a.k_cache != nullptr;  // the call appends (as opposed to rotating k in place)
 
   float cs[8], sn[8];
   if (rotate) {
@@ -196,7 +219,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
     }
   }
   // k: rotated, into the cache (or in place when there is no cache)
-  if (a.k != nullptr && (rotate || a.k_cache != nullptr)) {
+  if (a.k != nullptr && (to_cache ? cache_ok : rotate)) {
     const uint8_t* base = reinterpret_cast<const uint8_t*>(a.k) + 2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(l) * a.kv_stride[1]);
     for (int h = 0; h < a.n_kv_heads; ++h) {
       const uint8_t* row = base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
@@ -220,7 +243,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
     }
   }
   // v: copied into the cache
-  if (a.v != nullptr && a.v_cache != nullptr) {
+  if (a.v != nullptr && a.v_cache != nullptr && cache_ok) {
     const uint8_t* base = reinterpret_cast<const uint8_t*>(a.v) + 2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(l) * a.kv_stride[1]);
     for (int h = 0; h < a.n_kv_heads; ++h) {
       const uint8_t* row = base + 2 * static_cast<size_t>(h) * a.kv_stride[2];

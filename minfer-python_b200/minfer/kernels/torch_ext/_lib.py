@@ -16,6 +16,7 @@ F16 = 0
 BF16 = 1
 KV_16BIT = 0
 KV_Q8_0 = 1
+ABI_VERSION = 5
 
 EXPORTS = (
     "minfer_attn_prefill",
@@ -54,6 +55,8 @@ class PrefillParams(ctypes.Structure):
         ("flags", ctypes.c_int32),
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
+        ("max_ctas", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
     ]
 
 
@@ -81,6 +84,9 @@ class DecodeParams(ctypes.Structure):
         ("block_table", ctypes.c_void_p),
         ("page_size", ctypes.c_int32),
         ("table_stride", ctypes.c_int32),
+        ("n_pages", ctypes.c_int32),
+        ("flags", ctypes.c_int32),
+        ("status", ctypes.c_void_p),
     ]
 
 
@@ -110,6 +116,9 @@ class RopeParams(ctypes.Structure):
         ("block_table", ctypes.c_void_p),
         ("page_size", ctypes.c_int32),
         ("table_stride", ctypes.c_int32),
+        ("n_pages", ctypes.c_int32),
+        ("flags", ctypes.c_int32),
+        ("status", ctypes.c_void_p),
     ]
 
 
@@ -140,6 +149,9 @@ def _load() -> ctypes.CDLL:
     lib.minfer_attn_last_cuda_error.restype = ctypes.c_char_p
     lib.minfer_attn_abi_version.argtypes = []
     lib.minfer_attn_abi_version.restype = ctypes.c_int
+    if lib.minfer_attn_abi_version() != ABI_VERSION:
+        raise ImportError(f"{LIB_PATH} has ABI version {lib.minfer_attn_abi_version()}, this binding needs "
+                          f"{ABI_VERSION}: rebuild it with `python build.py --force`")
     return lib
 
 

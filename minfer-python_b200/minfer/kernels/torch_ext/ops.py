@@ -10,6 +10,7 @@ and the current CUDA stream to libminfer_attn.so; nothing here computes.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 
@@ -18,9 +19,21 @@ import torch
 from . import _lib
 
 _DEBUG = os.environ.get("MINFER_ATTN_DEBUG", "0") not in ("", "0")
-# cross-check aid: run the single-tile prefill kernel instead of the two-tile one
-_SIMPLE = os.environ.get("MINFER_ATTN_SIMPLE_KERNEL", "0") not in ("", "0")
-_FLAGS = int(os.environ.get("MINFER_ATTN_FLAGS", "0"))  # extra MINFER_ATTN_FLAG_* bits, for cross-checking
+_max_ctas = 0  # upper bound on the prefill grid (0: one thread block per SM), see prefill_cta_limit()
+
+
+@contextlib.contextmanager
+def prefill_cta_limit(n: int):
+    """Inside the block every prefill call launches at most `n` thread blocks (0 = one per SM).
+    The prefill kernel is persistent and fills every SM it is given; a caller that wants a kernel
+    of another stream to run beside it - the multi-GPU harness overlaps the output all-gather of
+    one row block with the attention of the next - leaves a few SMs free this way."""
+    global _max_ctas
+    old, _max_ctas = _max_ctas, int(n)
+    try:
+        yield
+    finally:
+        _max_ctas = old
 
 _DEFS = {
     "flash_attn": "(int qtype_int, int qblock_size, int qtype_size, Tensor q, Tensor k, Tensor v, "
@@ -61,14 +74,19 @@ def _status_word(device: torch.device) -> torch.Tensor:
 
 
 def check_status(device=None) -> None:
-    """Synchronise and raise if a kernel on `device` gave up a bounded wait."""
+    """Synchronise and raise if a kernel on `device` left a report in the status word: a bounded wait
+    that ran out (code 100), a block-table entry outside the page pool (101: sequence, table index,
+    entry) or a cache position outside [0, max_len) (102: sequence, position, max_len)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     t = _status_word(device)
     torch.cuda.synchronize(device)
     vals = t.tolist()
     if vals[0] != 0:
         t.zero_()
-        raise RuntimeError(f"minfer attention kernel reported status {vals} (code, block x, block y/z, wait site)")
+        what = {100: "a bounded wait ran out (code, block x, block y/z, wait site)",
+                101: "block-table entry outside the page pool (code, sequence, table index, entry)",
+                102: "cache position out of range (code, sequence, position, max_len)"}.get(vals[0], "unknown code")
+        raise RuntimeError(f"minfer attention kernel reported status {vals}: {what}")
 
 
 def _dtype_tag(t: torch.Tensor) -> int:
@@ -107,7 +125,8 @@ def _prefill(q, k, v, mask, out, causal: bool) -> None:
     p.dtype = _dtype_tag(q)
     p.causal = 1 if causal else 0
     p.softmax_scale = 0.0
-    p.flags = (1 if _SIMPLE else 0) | _FLAGS
+    p.flags = 0
+    p.max_ctas = _max_ctas
     # mask tile classes (dense mask) or the persistent kernel's work-item counter (causal)
     need = _lib.lib.minfer_attn_prefill_workspace_bytes(p.batch, p.seq_q, p.seq_k) if mask is not None else 16
     ws = _workspace_for(q.device, need, _mask_workspace, torch.cuda.current_stream(q.device).cuda_stream)
@@ -150,7 +169,8 @@ def _check_q8_cache(cache: torch.Tensor, batch: int, head_dim: int, what: str) -
     torch._check(cache.is_cuda and cache.dtype == torch.uint8 and cache.dim() == 4, lambda: f"{what} must be a CUDA uint8 [B, Hkv, Lmax, bytes] tensor")
     torch._check(cache.size(0) == batch and cache.size(3) == head_dim // 32 * 34, lambda: f"{what}: batch or row bytes do not match (row = head_dim/32 blocks of 34 bytes)")
     torch._check(cache.stride(3) == 1 and cache.stride(2) == cache.size(3), lambda: f"{what}: rows of one head must be contiguous")
-    torch._check(cache.size(2) % 2 == 0, lambda: f"{what}: the padded length must be even")
+    mult = 4 if head_dim == 64 else 2  # rows of one (batch, head) must end on a 16-byte boundary
+    torch._check(cache.size(2) % mult == 0, lambda: f"{what}: the padded length must be a multiple of {mult}")
 
 
 def _flash_attn_decode_q8_cuda(q, k_cache, v_cache, lens, out) -> None:
@@ -204,6 +224,8 @@ def _decode_call(q, k_cache, v_cache, lens, out, kv_format, block_table=None) ->
         p.block_table = block_table.data_ptr()
         p.page_size, p.table_stride = k_cache.size(2), block_table.size(1)
         p.max_len = p.page_size * p.table_stride
+        p.n_pages = k_cache.size(0)
+    p.status = _status_word(q.device).data_ptr()
     p.dtype = _dtype_tag(q)
     p.chunk = 0
     p.softmax_scale = 0.0
@@ -294,6 +316,8 @@ def _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache
         p.block_table = block_table.data_ptr()
         p.page_size, p.table_stride = k_cache.size(2), block_table.size(1)
         p.max_len = p.page_size * p.table_stride
+        p.n_pages = k_cache.size(0)
+    p.status = _status_word(q.device).data_ptr()
     p.dtype, p.style = _dtype_tag(q), style
     p.cache_format = _lib.KV_Q8_0 if q8 else _lib.KV_16BIT
     _rope_call(p, q.device)

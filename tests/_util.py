@@ -66,3 +66,19 @@ def check_close(actual: torch.Tensor, expected: torch.Tensor, what: str = "", bf
     assert not bad.any(), (f"{what}: {int(bad.sum())} of {bad.numel()} elements out of tolerance, "
                            f"max abs err {float(err.max()):.3e}")
     return float(err.max())
+
+
+def bf16_tolerance_counts(actual: torch.Tensor, expected: torch.Tensor) -> dict:
+    """How a bfloat16 result stands against the fp32 oracle, three ways: elements outside the plain
+    atol = rtol = 2e-3; outside it once half a bfloat16 ulp of the expected value is allowed (the check
+    the tests gate on); and elements where the oracle value ROUNDED to bfloat16 - the best any kernel
+    can return - is itself outside the plain tolerance."""
+    a = actual.detach().float().cpu()
+    e = expected.detach().float().cpu()
+    err = (a - e).abs()
+    tol = ATOL + RTOL * e.abs()
+    best = (e.to(torch.bfloat16).float() - e).abs()
+    return {"elements": e.numel(), "fail_plain_2e-3": int((err > tol).sum()),
+            "fail_with_half_ulp": int((err > tol + bf16_half_ulp(e)).sum()),
+            "rounded_oracle_fails_plain": int((best > tol).sum()), "max_abs_err": float(err.max()),
+            "max_abs_expected": float(e.abs().max())}

@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     from minfer.kernels.torch_ext import _lib
     for s in declared_symbols():
         assert hasattr(_lib.lib, s), f"{s} declared in the header but not exported"
-    assert _lib.lib.minfer_attn_abi_version() == 4
+    assert _lib.lib.minfer_attn_abi_version() == 5
     assert set(_lib.EXPORTS) <= set(declared_symbols())
 
 
@@ -99,3 +99,42 @@ def test_ops_have_no_cpu_path():
         k.flash_attn_causal(q, q, q, q.clone())
     with pytest.raises(ValueError):
         KernelBackend("triton")
+
+
+def test_reference_callers_find_their_imports():
+    """The reference's test file and apps begin with `from minfer.kernels import refs`, `from minfer.kernels
+    import KernelBackend`, `from minfer.const import GGMLQuantizationType, GGML_QUANT_SIZES` and (conftest)
+    `import minfer.kernels.torch_ext` (test/kernels.py:9-11, test/conftest.py:2, apps/benchmark.py:11-13):
+    all of them resolve against this package, the qtype the attention callers pass is an int-valued enum
+    member with the (1, 2) size pair, and refs.flash_attn is torch's SDPA on a bool mask."""
+    import torch
+    from minfer.kernels import refs
+    from minfer.kernels import KernelBackend
+    from minfer.const import GGMLQuantizationType, GGML_QUANT_SIZES
+    import minfer.kernels.torch_ext  # noqa: F401
+
+    kerns = KernelBackend("torch_ext")
+    assert callable(kerns.flash_attn) and callable(kerns.il_rope) and callable(kerns.neox_rope)
+    assert "flash_attn" in [k for k in vars(kerns) if not k.startswith("_")]   # the apps build --kernel choices this way
+    qtype = GGMLQuantizationType.F16
+    assert int(qtype) == 1 and GGML_QUANT_SIZES[qtype] == (1, 2)
+    with pytest.raises(ValueError):
+        KernelBackend("triton")
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(1, 2, 5, 8, generator=g) for _ in range(3))
+    mask = torch.tril(torch.ones(5, 5, dtype=torch.bool))[None, None]
+    want = torch.softmax((q @ k.transpose(-1, -2) / 8 ** 0.5).masked_fill(~mask, float("-inf")), -1) @ v
+    assert torch.allclose(refs.flash_attn(q, k, v, mask), want, atol=1e-6)
+    lens = torch.tensor([3])
+    assert torch.allclose(refs.flash_attn_decode(q[:, :, :1], k, v, lens),
+                          torch.softmax(q[:, :, :1] @ k[:, :, :3].transpose(-1, -2) / 8 ** 0.5, -1) @ v[:, :, :3], atol=1e-6)
+
+
+def test_refs_rope_matches_the_oracle_restatement():
+    import torch
+    from minfer.kernels import refs
+    from oracle import oracle as O
+    x = torch.randn(2, 5, 3, 64, generator=torch.Generator().manual_seed(1)).half()
+    for rot in (64, 32):
+        assert torch.allclose(refs.il_rope(x, rot, 7, 10000.0).float(), O.il_rope_reference(x, rot, 7, 10000.0).float(), atol=2e-3)
+        assert torch.allclose(refs.neox_rope(x, rot, 7, 10000.0).float(), O.neox_rope_reference(x, rot, 7, 10000.0).float(), atol=2e-3)

@@ -74,6 +74,7 @@ def test_paged_q8_through_the_c_abi(kerns):
     p.q, p.k_cache, p.v_cache, p.lens, p.out = qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), ld.data_ptr(), out_p.data_ptr()
     p.batch, p.n_heads, p.n_kv_heads, p.head_dim = B, H, Hkv, D
     p.page_size, p.table_stride, p.block_table = page, max_pages, td.data_ptr()
+    p.n_pages = n_pages
     p.max_len = page * max_pages
     p.dtype, p.chunk, p.softmax_scale, p.kv_format = _lib.F16, 0, 0.0, _lib.KV_Q8_0
     for i in range(2):
@@ -102,9 +103,45 @@ def test_paged_argument_errors():
     p.kv_stride[0], p.kv_stride[1], p.kv_stride[2] = 4096, 2048, 128
     p.workspace, p.workspace_bytes = buf.data_ptr(), buf.numel() * 2
     p.block_table = tab.data_ptr()
-    for page, stride, want in ((24, 8, 1), (0, 8, 1), (16, 0, 1), (16, 7, 1)):
-        p.page_size, p.table_stride = page, stride
-        assert _lib.lib.minfer_attn_decode(ctypes.byref(p), None) == want, (page, stride)   # MINFER_ATTN_EINVAL
+    for page, stride, n_pages, want in ((24, 8, 4, 1), (0, 8, 4, 1), (16, 0, 4, 1), (16, 7, 4, 1), (16, 8, 0, 1)):
+        p.page_size, p.table_stride, p.n_pages = page, stride, n_pages
+        assert _lib.lib.minfer_attn_decode(ctypes.byref(p), None) == want, (page, stride, n_pages)   # MINFER_ATTN_EINVAL
+
+
+def test_block_table_entry_outside_the_pool_is_reported_not_followed(kerns):
+    """A live table entry that points outside [0, n_pages): the kernel must not dereference it (it reads
+    page 0 instead, so nothing outside the pools is touched) and must say so through the status word; the
+    sequences with sound tables still get their results.  Same for the appending kernel: the row is
+    dropped, every page keeps its content."""
+    from minfer.kernels.torch_ext.ops import check_status
+    B, H, Hkv, D, page = 3, 8, 2, 128, 16
+    lens = torch.tensor([100, 40, 64], dtype=torch.int32)
+    kp, vp, table, kc, vc = make_paged(B, Hkv, D, page, lens, torch.float16, seed=77)
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(B, H, 1, D, generator=g).half()
+    want = O.decode_paged_oracle(q, kp, vp, table, lens)
+    bad = table.clone()
+    bad[1, 1] = kp.size(0) + 1000          # sequence 1, keys 16..31
+    out = torch.full(q.shape, float("nan"), dtype=torch.float16, device="cuda")
+    check_status()
+    kerns.flash_attn_decode_paged(q.cuda(), kp.cuda(), vp.cuda(), bad.cuda(), lens.cuda(), out)
+    with pytest.raises(RuntimeError, match="block-table entry"):
+        check_status()
+    check_status()                          # the report is cleared once read
+    assert torch.isfinite(out).all()
+    check_close(out[[0, 2]], want[[0, 2]], "sequences with sound tables")
+    # append through the same bad table: nothing is written for the bad row
+    kpd, vpd = kp.cuda(), vp.cuda()
+    before_k, before_v = kpd.clone(), vpd.clone()
+    qa = torch.randn(B, 1, H, D, generator=g).half().cuda()
+    ka = torch.randn(B, 1, Hkv, D, generator=g).half().cuda()
+    va = torch.randn(B, 1, Hkv, D, generator=g).half().cuda()
+    start = torch.tensor([0, 20, 0], dtype=torch.int32, device="cuda")   # sequence 1 -> table slot 1 (bad)
+    kerns.rope_kv_append_paged(D, 10000.0, 0, qa, ka, va, kpd, vpd, bad.cuda(), start)
+    with pytest.raises(RuntimeError, match="block-table entry"):
+        check_status()
+    changed = (kpd != before_k).flatten(1).any(1).nonzero().flatten().tolist()
+    assert sorted(changed) == sorted({int(bad[0, 0]), int(bad[2, 0])})
 
 
 def test_rope_append_into_pages_then_decode(kerns):

@@ -128,3 +128,25 @@ def test_q8_argument_errors(kerns):
         kerns.flash_attn_decode_q8(q, ok[:, :, :63], ok[:, :, :63], lens, torch.zeros_like(q))   # odd padded length
     with pytest.raises(RuntimeError):
         kerns.flash_attn_decode_q8(q, ok.half(), ok.half(), lens, torch.zeros_like(q))           # not uint8
+    # head_dim 64: rows are 68 bytes, so the padded length must be a multiple of 4 (62 is even but is refused)
+    q64 = torch.zeros(2, 8, 1, 64, dtype=torch.float16, device="cuda")
+    c64 = torch.zeros(2, 2, 64, 68, dtype=torch.uint8, device="cuda")
+    kerns.flash_attn_decode_q8(q64, c64, c64, lens, torch.zeros_like(q64))
+    with pytest.raises(RuntimeError):
+        kerns.flash_attn_decode_q8(q64, c64[:, :, :62].contiguous(), c64[:, :, :62].contiguous(), lens, torch.zeros_like(q64))
+
+
+@pytest.mark.parametrize("D,Lmax", [(64, 60), (64, 36), (128, 34)])
+def test_q8_full_length_sequences_at_the_end_of_the_allocation(kerns, D, Lmax):
+    """lens == max_len for every sequence, caches sized exactly: the last 16-byte copy of the last tile ends
+    where the allocation ends (the copies move whole 16-byte chunks of 68- or 136-byte rows)."""
+    B, H, Hkv = 2, 4, 2
+    g = torch.Generator().manual_seed(D + Lmax)
+    q = torch.randn(B, H, 1, D, generator=g).half()
+    kq, vq = make_q8_cache(B, Hkv, Lmax, D, 31), make_q8_cache(B, Hkv, Lmax, D, 32)
+    lens = torch.full((B,), Lmax, dtype=torch.int32)
+    out = torch.full((B, H, 1, D), float("nan"), dtype=torch.float16, device="cuda")
+    kerns.flash_attn_decode_q8(q.cuda(), kq.cuda(), vq.cuda(), lens.cuda(), out)
+    torch.cuda.synchronize()
+    kd, vd = O.q8_0_dequantize(kq, torch.float16), O.q8_0_dequantize(vq, torch.float16)
+    check_close(out, O.decode_oracle(q, kd, vd, lens), f"q8 full length D={D}")

@@ -29,7 +29,8 @@ def _worker(rank, world, port, result_dir):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        from minfer.dist import balanced_batch_shards, decode_batch_parallel, prefill_head_parallel
+        from minfer.dist import DecodeShards, decode_batch_parallel, head_shard, prefill_head_parallel
+        from minfer.kernels.torch_ext.ops import prefill_cta_limit
         from minfer.kernels import KernelBackend
         kerns = KernelBackend("torch_ext")
         g = torch.Generator().manual_seed(9)
@@ -37,19 +38,34 @@ def _worker(rank, world, port, result_dir):
         q = torch.randn(B, H, L, D, generator=g).half().cuda()
         k = torch.randn(B, Hkv, L, D, generator=g).half().cuda()
         v = torch.randn(B, Hkv, L, D, generator=g).half().cuda()
-        full = prefill_head_parallel(kerns.flash_attn_causal, q, k, v)
         single = torch.empty_like(q)
         kerns.flash_attn_causal(q, k, v, single)
+        for blocks in (1, 2):
+            full = prefill_head_parallel(kerns.flash_attn_causal, q, k, v, blocks=blocks)
+            torch.cuda.synchronize()
+            assert torch.equal(full, single), f"head-parallel prefill differs from the single-GPU result (blocks={blocks})"
+        # B = 1, this rank's slices only, a caller-owned output buffer, the exchange overlapped with the
+        # attention of the next block while the attention leaves 8 SMs to the exchange
+        qs, kvs = head_shard(H, Hkv, world, rank)
+        buf = torch.full((1, H, L, D), float("nan"), dtype=torch.float16, device="cuda")
+        with prefill_cta_limit(140):
+            prefill_head_parallel(kerns.flash_attn_causal, q[:1, qs].contiguous(), k[:1, kvs].contiguous(),
+                                  v[:1, kvs].contiguous(), out=buf, blocks=2, inputs_are_shards=True)
         torch.cuda.synchronize()
-        assert torch.equal(full, single), "head-parallel prefill differs from the single-GPU result"
+        assert torch.equal(buf, single[:1]), "B=1 shard inputs"
+        buf.fill_(float("nan"))
+        prefill_head_parallel(kerns.flash_attn_causal, q[:1], k[:1], v[:1], out=buf)
+        torch.cuda.synchronize()
+        assert torch.equal(buf, single[:1]), "B=1 in-place all-gather"
 
         Bd, Lmax = 8, 1500
         qd = torch.randn(Bd, H, 1, D, generator=g).half().cuda()
         kc = torch.randn(Bd, Hkv, Lmax, D, generator=g).half().cuda()
         vc = torch.randn(Bd, Hkv, Lmax, D, generator=g).half().cuda()
         lens = torch.tensor([1500, 3, 700, 1025, 64, 512, 513, 999], dtype=torch.int32).cuda()
-        shards = balanced_batch_shards(lens.tolist(), world)
-        outd = decode_batch_parallel(kerns.flash_attn_decode, qd, kc, vc, lens, shards)
+        shards = DecodeShards(lens.tolist(), world)
+        mine = torch.tensor(shards.mine(rank), device="cuda")
+        outd = decode_batch_parallel(kerns.flash_attn_decode, qd[mine], kc[mine], vc[mine], lens[mine].contiguous(), shards)
         single_d = torch.empty_like(qd)
         kerns.flash_attn_decode(qd, kc, vc, lens, single_d)
         torch.cuda.synchronize()

@@ -104,3 +104,28 @@ def test_rope_argument_errors(kerns):
         kerns.neox_rope(24, 0, 1e4, x)                                 # neox needs a multiple of 16
     with pytest.raises(RuntimeError):
         kerns.il_rope(64, 0, 1e4, x.float())                           # dtype
+
+
+def test_out_of_range_start_is_dropped_and_reported(kerns):
+    """start[b] + l outside [0, max_len): the row is not written anywhere (the neighbouring cache rows and
+    the other sequences keep their content), q is still rotated, and the status word names the sequence."""
+    from minfer.kernels.torch_ext.ops import check_status
+    B, L, H, Hkv, D, Lmax = 3, 2, 4, 2, 64, 32
+    g = torch.Generator().manual_seed(8)
+    q = torch.randn(B, L, H, D, generator=g).half().cuda()
+    k = torch.randn(B, L, Hkv, D, generator=g).half().cuda()
+    v = torch.randn(B, L, Hkv, D, generator=g).half().cuda()
+    kc = torch.full((B, Hkv, Lmax, D), 7.0, dtype=torch.float16, device="cuda")
+    vc = torch.full((B, Hkv, Lmax, D), 7.0, dtype=torch.float16, device="cuda")
+    start = torch.tensor([3, Lmax - 1, -1], dtype=torch.int32, device="cuda")   # seq 1: second token overflows; seq 2: first is negative
+    check_status()
+    kerns.rope_kv_append(D, 10000.0, 0, q, k, v, kc, vc, start)
+    with pytest.raises(RuntimeError, match="cache position out of range"):
+        check_status()
+    untouched = torch.ones(B, Lmax, dtype=torch.bool)
+    untouched[0, 3:5] = False
+    untouched[1, Lmax - 1] = False
+    untouched[2, 0] = False
+    wrote = (kc != 7.0).any(-1).any(1).cpu()           # [B, Lmax]
+    assert torch.equal(wrote, ~untouched)
+    assert torch.equal((vc != 7.0).any(-1).any(1).cpu(), ~untouched)
