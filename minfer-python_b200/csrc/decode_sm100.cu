@@ -14,6 +14,10 @@
 // 16 rows of m16n8k16 tensor-core tiles so the arithmetic stays far below the
 // memory time.  The warps' states are merged through shared memory and written
 // as one fp32 partial (max, sum, unnormalised output) per (query head, split).
+// The thread blocks of one (sequence, kv head) then take a ticket from a counter
+// in the workspace; whoever draws the last one merges the partials of all splits
+// (in split order, so the result does not depend on who that is) and writes the
+// 16-bit output.  Nobody waits for anybody: one launch, no second kernel.
 //
 // Q8 = true: the caches hold GGML Q8_0 blocks (32 int8 + one fp16 scale, 34 bytes;
 // the reference's block_q8_0, src/minfer/kernels/torch_ext/csrc/common/types.hpp:141-146).
@@ -23,8 +27,6 @@
 // does ((half)(q * d), csrc/quants/impl.cpp:1153-1166), and the arithmetic above
 // runs unchanged.  Cache bytes per key drop from 4 D to 2.125 D.
 //
-// Kernel 2 (decode_combine_kernel): grid (n_heads, batch) merges the partials
-// of the ceil(len / chunk) splits of a sequence and writes the 16-bit output.
 #include "attn_internal.h"
 #include "ptx.cuh"
 
@@ -122,6 +124,16 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
 
   const int len = min(a.lens[b], a.max_len);
   const int c0 = split * a.chunk;
+  if (len <= 0 && split == 0) {
+    // an empty sequence has no split to merge: its output rows are zeros
+    for (int idx = tid; idx < a.group * D; idx += kWarps * 32) {
+      const int h = kvh * a.group + idx / D;
+      uint8_t* op = reinterpret_cast<uint8_t*>(a.out) +
+                    2 * (static_cast<size_t>(b) * a.out_stride[0] + static_cast<size_t>(h) * a.out_stride[1] + idx % D);
+      *reinterpret_cast<uint16_t*>(op) = 0;
+    }
+    return;
+  }
   if (c0 >= len) return;
   const int c1 = min(len, c0 + a.chunk);
   const int nt = (c1 - c0 + kTileKeys - 1) / kTileKeys;
@@ -386,29 +398,39 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
       a.part_ml[pidx * 2 + 1] = l;
     }
   }
-}
 
-template <int D, bool BF16>
-__global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
-  const int h = blockIdx.x;
-  const int b = blockIdx.y;
-  const int d = threadIdx.x;
-  const int len = min(a.lens[b], a.max_len);
-  const int ns = (len + a.chunk - 1) / a.chunk;
-  const size_t p0 = (static_cast<size_t>(b) * a.n_heads + h) * a.n_split;
-  float M = -INFINITY;
-  for (int s = 0; s < ns; ++s) M = fmaxf(M, a.part_ml[(p0 + s) * 2]);
-  float o = 0.f, l = 0.f;
-  for (int s = 0; s < ns; ++s) {
-    const float sc = ex2_approx(a.part_ml[(p0 + s) * 2] - M);
-    l += sc * a.part_ml[(p0 + s) * 2 + 1];
-    o += sc * a.part_o[(p0 + s) * D + d];
+  // ---- ticket: the last thread block of this (sequence, kv head) merges the splits ----
+  const int n_live = (len + a.chunk - 1) / a.chunk;
+  __shared__ int s_last;
+  __threadfence();   // this block's partials are visible device-wide before its ticket is
+  __syncthreads();
+  if (tid == 0) {
+    int* ticket = a.tickets + static_cast<size_t>(b) * a.n_kv_heads + kvh;
+    const int t = atomicAdd(ticket, 1);
+    s_last = (t == n_live - 1) ? 1 : 0;
+    if (s_last) *ticket = 0;  // left as found: zero
   }
-  const float r = (l > 0.f) ? o / l : 0.f;
-  uint8_t* op = reinterpret_cast<uint8_t*>(a.out) +
-                2 * (static_cast<size_t>(b) * a.out_stride[0] + static_cast<size_t>(h) * a.out_stride[1] + d);
-  if constexpr (BF16) *reinterpret_cast<__nv_bfloat16*>(op) = __float2bfloat16_rn(r);
-  else *reinterpret_cast<__half*>(op) = __float2half_rn(r);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();   // the other blocks' partials, written before their tickets, are visible now
+  for (int idx = tid; idx < a.group * D; idx += kWarps * 32) {
+    const int h = kvh * a.group + idx / D;
+    const int d = idx % D;
+    const size_t p0 = (static_cast<size_t>(b) * a.n_heads + h) * a.n_split;
+    float M = -INFINITY;
+    for (int s = 0; s < n_live; ++s) M = fmaxf(M, __ldcg(&a.part_ml[(p0 + s) * 2]));
+    float o = 0.f, l = 0.f;
+    for (int s = 0; s < n_live; ++s) {
+      const float sc = ex2_approx(__ldcg(&a.part_ml[(p0 + s) * 2]) - M);
+      l += sc * __ldcg(&a.part_ml[(p0 + s) * 2 + 1]);
+      o += sc * __ldcg(&a.part_o[(p0 + s) * D + d]);
+    }
+    const float r = (l > 0.f) ? o / l : 0.f;
+    uint8_t* op = reinterpret_cast<uint8_t*>(a.out) +
+                  2 * (static_cast<size_t>(b) * a.out_stride[0] + static_cast<size_t>(h) * a.out_stride[1] + d);
+    if constexpr (BF16) *reinterpret_cast<__nv_bfloat16*>(op) = __float2bfloat16_rn(r);
+    else *reinterpret_cast<__half*>(op) = __float2half_rn(r);
+  }
 }
 
 template <int D, bool BF16, bool Q8, bool Paged>
@@ -425,11 +447,12 @@ cudaError_t launch_paged(const DecodeArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
+  // the ticket counters start at zero (the kernel also leaves them at zero, but the workspace is the
+  // caller's and may hold anything on first use)
+  e = cudaMemsetAsync(a.tickets, 0, sizeof(int) * static_cast<size_t>(a.batch) * a.n_kv_heads, stream);
+  if (e != cudaSuccess) return e;
   dim3 grid(a.n_split, a.n_kv_heads, a.batch);
   decode_split_kernel<D, BF16, Q8, Paged><<<grid, kWarps * 32, smem, stream>>>(a);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-  decode_combine_kernel<D, BF16><<<dim3(a.n_heads, a.batch), D, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

@@ -1,0 +1,248 @@
+// CUDA implementations of the attention ops, bound through LibTorch's stable ABI.
+//
+// Counterpart of the reference's src/minfer/kernels/torch_ext/csrc/cuda/reg.cu:16-27
+// (STABLE_TORCH_LIBRARY_IMPL(minfer, CUDA, m) + TORCH_BOX(&flash_attn_cuda)) and of its launcher
+// csrc/cuda/flash_attn/op.cuh:21-106: the same checks in the same order (devices, innermost
+// stride 1 and k/v sharing strides, dtypes, ranks, shapes), the QKVStrides capture (:80-83), the
+// current stream of the current device from the shim (:98-103) - and then, where the reference
+// stops at "TODO: implement", one call into the C ABI of libminfer_attn.so.  Relaxed against the
+// reference only as the benchmark configurations demand: bfloat16 next to float16, head_dim 64
+// next to 128 (both enforced by the library, not here).
+//
+// No device code lives in this unit; it is compiled by the host compiler.
+#include <torch/csrc/stable/accelerator.h>
+#include <torch/csrc/stable/library.h>
+#include <torch/csrc/stable/ops.h>
+#include <torch/csrc/stable/tensor.h>
+#include <torch/csrc/stable/macros.h>
+#include <torch/headeronly/core/ScalarType.h>
+#include <torch/headeronly/macros/Macros.h>
+
+#include <torch/csrc/stable/c/shim.h>
+
+#include <array>
+#include <map>
+#include <mutex>
+#include <string>
+#include <utility>
+
+#include "../../../include/minfer_attn.h"
+
+namespace minfer {
+
+using torch::headeronly::DeviceType;
+using torch::headeronly::ScalarType;
+using torch::stable::Tensor;
+
+namespace {
+
+void* current_stream() {
+  auto device_index = torch::stable::accelerator::getCurrentDeviceIndex();
+  void* stream_ptr = nullptr;
+  TORCH_ERROR_CODE_CHECK(aoti_torch_get_current_cuda_stream(device_index, &stream_ptr));
+  return stream_ptr;
+}
+
+// Device buffers this layer owns (the library itself allocates nothing): one status word per
+// device, one scratch buffer per (device, stream, purpose), grown on demand through torch's
+// allocator and kept for the life of the process.
+std::mutex g_mu;
+std::map<int, Tensor*> g_status;
+std::map<std::array<int64_t, 3>, Tensor*> g_scratch;
+int g_max_ctas = 0;
+
+Tensor& status_word(const Tensor& like) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  const int dev = like.get_device_index();
+  auto it = g_status.find(dev);
+  if (it == g_status.end()) {
+    const int64_t n[1] = {4};
+    it = g_status.emplace(dev, new Tensor(torch::stable::new_zeros(like, {n, 1}, ScalarType::Int))).first;
+  }
+  return *it->second;
+}
+
+Tensor& scratch(const Tensor& like, void* stream, int64_t purpose, size_t bytes) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  const std::array<int64_t, 3> key = {like.get_device_index(), reinterpret_cast<int64_t>(stream), purpose};
+  auto it = g_scratch.find(key);
+  if (it == g_scratch.end() || static_cast<size_t>(it->second->numel()) < bytes) {
+    const int64_t n[1] = {static_cast<int64_t>(bytes < (1u << 20) ? (1u << 20) : bytes)};
+    Tensor* t = new Tensor(torch::stable::new_empty(like, {n, 1}, ScalarType::Byte));
+    if (it == g_scratch.end()) it = g_scratch.emplace(key, t).first;
+    else it->second = t;  // the old buffer stays alive: launches in flight may still use it
+  }
+  return *it->second;
+}
+
+int dtype_tag(const Tensor& t) {
+  const auto st = t.scalar_type();
+  STD_TORCH_CHECK(st == ScalarType::Half || st == ScalarType::BFloat16, "minfer attention: float16 or bfloat16 tensors expected");
+  return st == ScalarType::Half ? MINFER_ATTN_F16 : MINFER_ATTN_BF16;
+}
+
+void check_rc(int rc, const char* what) {
+  if (rc == MINFER_ATTN_OK) return;
+  std::string msg = std::string(what) + ": " + minfer_attn_strerror(rc);
+  if (rc == MINFER_ATTN_ECUDA) msg += std::string(" [") + minfer_attn_last_cuda_error() + "]";
+  STD_TORCH_CHECK(false, msg);
+}
+
+void check_qkv(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out) {
+  STD_TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda() && out.is_cuda(), "all tensors must be on CUDA");
+  STD_TORCH_CHECK(q.get_device_index() == k.get_device_index() && q.get_device_index() == v.get_device_index() &&
+                  q.get_device_index() == out.get_device_index(), "tensors on different devices");
+  STD_TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4 && out.dim() == 4, "tensors must be 4-D");
+  STD_TORCH_CHECK(q.stride(-1) == 1 && k.stride(-1) == 1 && v.stride(-1) == 1 && out.stride(-1) == 1 &&
+                  k.stride(0) == v.stride(0) && k.stride(1) == v.stride(1) && k.stride(2) == v.stride(2),
+                  "innermost stride must be 1 and k, v must share strides");
+  STD_TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type() &&
+                  q.scalar_type() == out.scalar_type(), "q, k, v, out must share one dtype");
+  STD_TORCH_CHECK(q.sizes().equals(out.sizes()), "q and out shapes differ");
+  STD_TORCH_CHECK(k.sizes().equals(v.sizes()), "k and v shapes differ");
+  STD_TORCH_CHECK(q.size(0) == k.size(0) && q.size(3) == k.size(3), "batch or head_dim mismatch");
+  STD_TORCH_CHECK(q.size(1) % k.size(1) == 0, "n_heads must be a multiple of n_kv_heads");
+}
+
+void prefill(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor* mask, Tensor& out, bool causal) {
+  MinferAttnPrefillParams p{};
+  p.q = q.const_data_ptr();
+  p.k = k.const_data_ptr();
+  p.v = v.const_data_ptr();
+  p.out = out.mutable_data_ptr();
+  p.mask = mask != nullptr ? static_cast<const uint8_t*>(mask->const_data_ptr()) : nullptr;
+  p.status = static_cast<int32_t*>(status_word(q).mutable_data_ptr());
+  for (int i = 0; i < 3; ++i) {
+    p.q_stride[i] = q.stride(i);
+    p.kv_stride[i] = k.stride(i);
+    p.out_stride[i] = out.stride(i);
+  }
+  p.batch = static_cast<int32_t>(q.size(0));
+  p.n_heads = static_cast<int32_t>(q.size(1));
+  p.n_kv_heads = static_cast<int32_t>(k.size(1));
+  p.seq_q = static_cast<int32_t>(q.size(2));
+  p.seq_k = static_cast<int32_t>(k.size(2));
+  p.head_dim = static_cast<int32_t>(q.size(3));
+  p.dtype = dtype_tag(q);
+  p.causal = causal ? 1 : 0;
+  p.max_ctas = g_max_ctas;
+  void* stream = current_stream();
+  const size_t need = mask != nullptr ? minfer_attn_prefill_workspace_bytes(p.batch, p.seq_q, p.seq_k) : 16;
+  Tensor& ws = scratch(q, stream, /*purpose=*/0, need);
+  p.workspace = ws.mutable_data_ptr();
+  p.workspace_bytes = static_cast<size_t>(ws.numel());
+  check_rc(minfer_attn_prefill(&p, stream), "minfer_attn_prefill");
+}
+
+void decode(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor* table, const Tensor& lens, Tensor& out,
+            int kv_format) {
+  STD_TORCH_CHECK(lens.is_cuda() && lens.get_device_index() == q.get_device_index(), "lens must be on the same CUDA device");
+  STD_TORCH_CHECK(lens.scalar_type() == ScalarType::Int && lens.dim() == 1 && lens.is_contiguous(),
+                  "lens must be a contiguous int32 vector");
+  STD_TORCH_CHECK(lens.numel() == q.size(0), "lens must have one entry per sequence");
+  STD_TORCH_CHECK(q.size(2) == 1, "decode takes one query token per sequence");
+  MinferAttnDecodeParams p{};
+  p.q = q.const_data_ptr();
+  p.k_cache = kc.const_data_ptr();
+  p.v_cache = vc.const_data_ptr();
+  p.lens = static_cast<const int32_t*>(lens.const_data_ptr());
+  p.out = out.mutable_data_ptr();
+  p.batch = static_cast<int32_t>(q.size(0));
+  p.n_heads = static_cast<int32_t>(q.size(1));
+  p.n_kv_heads = static_cast<int32_t>(kc.size(1));
+  p.max_len = static_cast<int32_t>(kc.size(2));
+  p.head_dim = static_cast<int32_t>(q.size(3));
+  if (table != nullptr) {
+    p.block_table = static_cast<const int32_t*>(table->const_data_ptr());
+    p.page_size = static_cast<int32_t>(kc.size(2));
+    p.table_stride = static_cast<int32_t>(table->size(1));
+    p.max_len = p.page_size * p.table_stride;
+    p.n_pages = static_cast<int32_t>(kc.size(0));
+  }
+  p.status = static_cast<int32_t*>(status_word(q).mutable_data_ptr());
+  p.dtype = dtype_tag(q);
+  p.kv_format = kv_format;
+  for (int i = 0; i < 2; ++i) {
+    p.q_stride[i] = q.stride(i);
+    p.out_stride[i] = out.stride(i);
+  }
+  for (int i = 0; i < 3; ++i) p.kv_stride[i] = kc.stride(i);
+  void* stream = current_stream();
+  const size_t need = minfer_attn_decode_workspace_bytes(p.batch, p.n_heads, p.max_len, p.head_dim, 0);
+  Tensor& ws = scratch(q, stream, /*purpose=*/1, need);
+  p.workspace = ws.mutable_data_ptr();
+  p.workspace_bytes = static_cast<size_t>(ws.numel());
+  check_rc(minfer_attn_decode(&p, stream), "minfer_attn_decode");
+}
+
+}  // namespace
+
+void flash_attn_cuda(int64_t qtype_int, int64_t qblock_size, int64_t qtype_size,
+                     const Tensor& q,  // [B, n_heads, L, head_dim]
+                     const Tensor& k,  // [B, n_kv_heads, L, head_dim]
+                     const Tensor& v,  // [B, n_kv_heads, L, head_dim]
+                     Tensor& mask,     // [B, 1, L, L] bool, contiguous
+                     Tensor& out) {    // [B, n_heads, L, head_dim]
+  (void)qtype_int;
+  (void)qblock_size;
+  (void)qtype_size;
+  check_qkv(q, k, v, out);
+  STD_TORCH_CHECK(mask.is_cuda() && mask.get_device_index() == q.get_device_index(), "mask must be on the same CUDA device");
+  STD_TORCH_CHECK(mask.scalar_type() == ScalarType::Bool, "mask must be bool");
+  STD_TORCH_CHECK(mask.dim() == 4 && mask.is_contiguous(), "mask must be a contiguous 4-D tensor");
+  STD_TORCH_CHECK(q.size(2) == k.size(2), "flash_attn requires seq_q == seq_k");
+  STD_TORCH_CHECK(mask.size(0) == q.size(0) && mask.size(1) == 1 && mask.size(2) == q.size(2) && mask.size(3) == k.size(2),
+                  "mask must be [B, 1, L, L]");
+  prefill(q, k, v, &mask, out, /*causal=*/false);
+}
+
+void flash_attn_causal_cuda(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& out) {
+  check_qkv(q, k, v, out);
+  STD_TORCH_CHECK(k.size(2) >= q.size(2), "causal attention requires seq_k >= seq_q");
+  prefill(q, k, v, nullptr, out, /*causal=*/true);
+}
+
+void flash_attn_decode_cuda(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& lens, Tensor& out) {
+  check_qkv(q, k_cache, v_cache, out);
+  decode(q, k_cache, v_cache, nullptr, lens, out, MINFER_ATTN_KV_16BIT);
+}
+
+void flash_attn_decode_paged_cuda(const Tensor& q, const Tensor& k_pages, const Tensor& v_pages, const Tensor& block_table,
+                                  const Tensor& lens, Tensor& out) {
+  STD_TORCH_CHECK(q.is_cuda() && out.is_cuda() && q.dim() == 4 && out.dim() == 4 && q.sizes().equals(out.sizes()),
+                  "q/out must be CUDA [B, H, 1, D] tensors");
+  STD_TORCH_CHECK(out.scalar_type() == q.scalar_type(), "q/out must share one dtype");
+  STD_TORCH_CHECK(k_pages.is_cuda() && v_pages.is_cuda() && k_pages.dim() == 4 && v_pages.dim() == 4,
+                  "the page pools must be CUDA [n_pages, n_kv_heads, page_size, D] tensors");
+  STD_TORCH_CHECK(k_pages.scalar_type() == q.scalar_type() && v_pages.scalar_type() == q.scalar_type(),
+                  "the page pools must have q's dtype");
+  STD_TORCH_CHECK(k_pages.sizes().equals(v_pages.sizes()) && k_pages.strides().equals(v_pages.strides()),
+                  "the page pools must share shape and strides");
+  STD_TORCH_CHECK(k_pages.size(3) == q.size(3) && k_pages.stride(-1) == 1 && q.stride(-1) == 1 && out.stride(-1) == 1,
+                  "head_dim mismatch or innermost stride not 1");
+  STD_TORCH_CHECK(k_pages.size(2) % 16 == 0, "page_size must be a multiple of 16");
+  STD_TORCH_CHECK(q.size(1) % k_pages.size(1) == 0, "n_heads must be a multiple of n_kv_heads");
+  STD_TORCH_CHECK(block_table.is_cuda() && block_table.scalar_type() == ScalarType::Int && block_table.dim() == 2 &&
+                  block_table.is_contiguous() && block_table.size(0) == q.size(0),
+                  "block_table must be a contiguous CUDA int32 [B, max_pages] tensor");
+  decode(q, k_pages, v_pages, &block_table, lens, out, MINFER_ATTN_KV_16BIT);
+}
+
+Tensor attn_status_word_cuda(const Tensor& like) { return status_word(like); }
+
+void attn_set_prefill_cta_limit_cuda(const Tensor& like, int64_t max_ctas) {
+  (void)like;
+  STD_TORCH_CHECK(max_ctas >= 0, "max_ctas must be >= 0");
+  g_max_ctas = static_cast<int>(max_ctas);
+}
+
+STABLE_TORCH_LIBRARY_IMPL(minfer, CUDA, m) {
+  m.impl("flash_attn", TORCH_BOX(&flash_attn_cuda));
+  m.impl("flash_attn_causal", TORCH_BOX(&flash_attn_causal_cuda));
+  m.impl("flash_attn_decode", TORCH_BOX(&flash_attn_decode_cuda));
+  m.impl("flash_attn_decode_paged", TORCH_BOX(&flash_attn_decode_paged_cuda));
+  m.impl("attn_status_word", TORCH_BOX(&attn_status_word_cuda));
+  m.impl("attn_set_prefill_cta_limit", TORCH_BOX(&attn_set_prefill_cta_limit_cuda));
+}
+
+}  // namespace minfer

@@ -7,6 +7,15 @@ dsuarez01/minfer-python) and the argument checks of its launcher
 head_dim 64.  `flash_attn_causal` and `flash_attn_decode` are additions the
 reference has no counterpart for.  Every op forwards raw pointers, strides
 and the current CUDA stream to libminfer_attn.so; nothing here computes.
+
+Two bindings reach the library.  When the torch extension `_C` has been built
+(csrc/torch_binding: schemas and CUDA implementations registered through
+LibTorch's stable ABI, the reference's own mechanism, csrc/reg.cpp:21-33 and
+csrc/cuda/reg.cu:16-27) the attention ops dispatch into it and this module
+only adds the fake implementations and the ops it does not cover.  Otherwise -
+or with MINFER_ATTN_BINDING=ctypes - the schemas are defined here with
+torch.library and every op is a Python function that fills the C-ABI structs
+through ctypes.  Both paths end in the same extern "C" entry points.
 """
 from __future__ import annotations
 
@@ -30,10 +39,17 @@ def prefill_cta_limit(n: int):
     one row block with the attention of the next - leaves a few SMs free this way."""
     global _max_ctas
     old, _max_ctas = _max_ctas, int(n)
+    _push_cta_limit()
     try:
         yield
     finally:
         _max_ctas = old
+        _push_cta_limit()
+
+
+def _push_cta_limit() -> None:
+    if _C is not None:
+        torch.ops.minfer.attn_set_prefill_cta_limit.default(torch.empty(0, device="cuda"), _max_ctas)
 
 _DEFS = {
     "flash_attn": "(int qtype_int, int qblock_size, int qtype_size, Tensor q, Tensor k, Tensor v, "
@@ -55,9 +71,27 @@ _DEFS = {
     "rope_kv_append_q8": "(int rotary_dim, float freq_base, int style, Tensor(a!) q, Tensor k, Tensor v, "
                          "Tensor(a!) k_cache, Tensor(a!) v_cache, Tensor start) -> ()",
 }
-_library = torch.library.Library("minfer", "FRAGMENT")
-for _name, _schema in _DEFS.items():
-    _library.define(_name + _schema)
+_binding_choice = os.environ.get("MINFER_ATTN_BINDING", "auto")
+if _binding_choice not in ("auto", "ctypes", "stable"):
+    raise ImportError(f"MINFER_ATTN_BINDING={_binding_choice!r}: expected auto, ctypes or stable")
+_C = None
+if _binding_choice != "ctypes":
+    try:
+        from . import _C  # noqa: F401  (loading it registers the schemas and the C++ CUDA implementations)
+    except ImportError:
+        if _binding_choice == "stable":
+            raise
+        _C = None
+BINDING = "stable" if _C is not None else "ctypes"
+# ops whose CUDA implementation lives in the extension
+_IN_EXTENSION = ("flash_attn", "flash_attn_causal", "flash_attn_decode", "flash_attn_decode_paged") if _C is not None else ()
+
+if _C is None:
+    _library = torch.library.Library("minfer", "FRAGMENT")
+    for _name, _schema in _DEFS.items():
+        _library.define(_name + _schema)
+else:
+    _library = torch.library.Library("minfer", "IMPL")
 
 _status: dict[int, torch.Tensor] = {}
 _workspace: dict[int, torch.Tensor] = {}        # decode split-KV partials, per device
@@ -68,7 +102,10 @@ def _status_word(device: torch.device) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     t = _status.get(idx)
     if t is None:
-        t = torch.zeros(4, dtype=torch.int32, device=device)
+        if _C is not None:   # one word per device, shared with the extension's launches
+            t = torch.ops.minfer.attn_status_word.default(torch.empty(0, device=torch.device("cuda", idx)))
+        else:
+            t = torch.zeros(4, dtype=torch.int32, device=device)
         _status[idx] = t
     return t
 
@@ -323,16 +360,13 @@ def _rope_kv_append_cuda(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache
     _rope_call(p, q.device)
 
 
-_library.impl("il_rope", _il_rope_cuda, "CUDA")
-_library.impl("neox_rope", _neox_rope_cuda, "CUDA")
-_library.impl("rope_kv_append", _rope_kv_append_cuda, "CUDA")
-_library.impl("rope_kv_append_q8", _rope_kv_append_q8_cuda, "CUDA")
-_library.impl("rope_kv_append_paged", _rope_kv_append_paged_cuda, "CUDA")
-_library.impl("flash_attn_decode_q8", _flash_attn_decode_q8_cuda, "CUDA")
-_library.impl("flash_attn", _flash_attn_cuda, "CUDA")
-_library.impl("flash_attn_causal", _flash_attn_causal_cuda, "CUDA")
-_library.impl("flash_attn_decode", _flash_attn_decode_cuda, "CUDA")
-_library.impl("flash_attn_decode_paged", _flash_attn_decode_paged_cuda, "CUDA")
+for _name, _fn in (("il_rope", _il_rope_cuda), ("neox_rope", _neox_rope_cuda), ("rope_kv_append", _rope_kv_append_cuda),
+                   ("rope_kv_append_q8", _rope_kv_append_q8_cuda), ("rope_kv_append_paged", _rope_kv_append_paged_cuda),
+                   ("flash_attn_decode_q8", _flash_attn_decode_q8_cuda), ("flash_attn", _flash_attn_cuda),
+                   ("flash_attn_causal", _flash_attn_causal_cuda), ("flash_attn_decode", _flash_attn_decode_cuda),
+                   ("flash_attn_decode_paged", _flash_attn_decode_paged_cuda)):
+    if _name not in _IN_EXTENSION:
+        _library.impl(_name, _fn, "CUDA")
 
 
 def flash_attn(
@@ -516,3 +550,13 @@ def _(q, k_cache, v_cache, lens, out):
     torch._check(q.device.type == "cuda")
     torch._check(q.dim() == 4 and k_cache.dim() == 4 and v_cache.dim() == 4 and out.dim() == 4)
     torch._check(lens.dim() == 1)
+
+
+@torch.library.register_fake("minfer::attn_status_word") if _C is not None else (lambda f: f)
+def _(like):
+    return torch.empty(4, dtype=torch.int32, device=like.device)
+
+
+@torch.library.register_fake("minfer::attn_set_prefill_cta_limit") if _C is not None else (lambda f: f)
+def _(like, max_ctas):
+    return None
