@@ -15,13 +15,13 @@ import os
 import sys
 
 import torch
-import torch.nn.functional as F
 from torch.utils.benchmark import Compare, Timer
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from minfer.const import GGML_QUANT_SIZES, GGMLQuantizationType  # noqa: E402
 from minfer.kernels import KernelBackend  # noqa: E402
+from minfer.kernels import refs  # noqa: E402
 
 
 def _views(B, L, n_heads, n_kv_heads, head_dim):
@@ -58,7 +58,7 @@ def flash_attn(backend: str, which: str, causal_entry: bool = False):
                 kerns.flash_attn(qtype, qblock_size, qtype_size, Q, K, V, mask, out)
 
         def ref_flash_attn():
-            F.scaled_dot_product_attention(Q, K_exp, V_exp, attn_mask=mask)
+            refs.flash_attn(Q, K_exp, V_exp, mask)
 
         fn = my_flash_attn if which == "minfer" else ref_flash_attn
         timer = Timer(stmt="fn(); torch.cuda.synchronize()", globals={"fn": fn, "torch": torch},
@@ -89,13 +89,12 @@ def flash_attn_decode(backend: str, which: str):
     vc = torch.randn(B, Hkv, Lmax, D, dtype=torch.float16, device="cuda")
     out = torch.zeros_like(q)
     ld = lens.cuda()
-    mask = (torch.arange(Lmax)[None, :] < lens[:, None].long())[:, None, None, :].cuda()
 
     def mine():
         kerns.flash_attn_decode(q, kc, vc, ld, out)
 
     def ref():
-        F.scaled_dot_product_attention(q, kc, vc, attn_mask=mask, enable_gqa=True)
+        refs.flash_attn_decode(q, kc, vc, ld)
 
     fn = mine if which == "minfer" else ref
     m = Timer(stmt="fn(); torch.cuda.synchronize()", globals={"fn": fn, "torch": torch}, label="flash_attn_decode",
@@ -107,9 +106,12 @@ def flash_attn_decode(backend: str, which: str):
 
 if __name__ == "__main__":
     KERNELS = {"flash_attn": flash_attn, "flash_attn_causal": flash_attn_causal, "flash_attn_decode": flash_attn_decode}
+    # the reference's two-stage parse (apps/benchmark.py:282-289): --kernel offers the public attributes of the backend
     parser = argparse.ArgumentParser()
     parser.add_argument("--backend", choices=["torch_ext"], default="torch_ext")
-    parser.add_argument("--kernel", choices=sorted(KERNELS), required=True)
+    args, _ = parser.parse_known_args()
+    parser.add_argument("--kernel", choices=[k for k in vars(KernelBackend(args.backend)) if not k.startswith("_") and k in KERNELS],
+                        required=True)
     parser.add_argument("--which", choices=["minfer", "ref"], required=True)
     args = parser.parse_args()
     KERNELS[args.kernel](backend=args.backend, which=args.which)

@@ -2,9 +2,8 @@
 
 Same role and flags as the reference's apps/profile.py (apps/profile.py:96-143 of
 dsuarez01/minfer-python: one un-timed call per kernel under torch.no_grad()), with
-shape flags added so a capture can run on a small case.  Only the CUDA library is
-driven here; there is no `--which ref` leg because the PyTorch reference is not
-part of this package.
+shape flags added so a capture can run on a small case.  `--which ref` launches
+torch's SDPA through refs.flash_attn, as the reference's script does.
 
     python apps/profile.py --kernel flash_attn_causal --batch 2 --seq 4096 --calls 3
 """
@@ -18,6 +17,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from minfer.const import GGML_QUANT_SIZES, GGMLQuantizationType  # noqa: E402
 from minfer.kernels import KernelBackend  # noqa: E402
+from minfer.kernels import refs  # noqa: E402
 
 
 def _qkv(args, dtype):
@@ -42,6 +42,10 @@ def flash_attn(kerns, args, dtype):
     mask = (torch.arange(L, device="cuda").unsqueeze(0) <= torch.arange(L, device="cuda").unsqueeze(1))
     mask = mask.unsqueeze(0).unsqueeze(0).expand(args.batch, 1, L, L).to(torch.bool).contiguous()
     out = torch.zeros((args.batch, args.heads, L, args.head_dim), dtype=dtype, device="cuda")
+    if args.which == "ref":
+        n_rep = args.heads // args.kv_heads
+        k_exp, v_exp = k.repeat_interleave(n_rep, dim=1), v.repeat_interleave(n_rep, dim=1)
+        return lambda: refs.flash_attn(q, k_exp, v_exp, mask)
     return lambda: kerns.flash_attn(qtype, qblock_size, qtype_size, q, k, v, mask, out)
 
 
@@ -69,7 +73,7 @@ if __name__ == "__main__":
     parser = argparse.ArgumentParser()
     parser.add_argument("--backend", choices=["torch_ext"], default="torch_ext")
     parser.add_argument("--kernel", choices=sorted(KERNELS), required=True)
-    parser.add_argument("--which", choices=["minfer"], default="minfer")
+    parser.add_argument("--which", choices=["minfer", "ref"], default="minfer")
     parser.add_argument("--batch", type=int, default=4)
     parser.add_argument("--seq", type=int, default=4096, help="sequence length (prefill) or padded cache length (decode)")
     parser.add_argument("--heads", type=int, default=32)

@@ -268,10 +268,21 @@ def q8_0_dequantize_ref(qb: torch.Tensor, dtype=torch.float16) -> torch.Tensor:
     return out
 
 
-def build_ref(reference_root: str = "/root/reference") -> bool:
+def find_reference_root(reference_root=None):
+    """Where the reference's source tree is mounted, or None: the argument, else $MINFER_REFERENCE_ROOT, else
+    a checkout named `reference` beside this repository."""
+    candidates = [reference_root, os.environ.get("MINFER_REFERENCE_ROOT"),
+                  os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in candidates:
+        if c and os.path.exists(os.path.join(c, "src", "minfer", "kernels", "torch_ext", "csrc", "quants", "impl.cpp")):
+            return c
+    return None
+
+
+def build_ref(reference_root=None) -> bool:
     """Compile the reference's quant codec from its own sources (only where the reference tree exists)."""
-    src = os.path.join(reference_root, "src", "minfer", "kernels", "torch_ext", "csrc", "quants", "impl.cpp")
-    if not os.path.exists(src):
+    reference_root = find_reference_root(reference_root)
+    if reference_root is None:
         return reference_build_available()
     rc = subprocess.run(["make", "-C", _HERE, "_ref", f"REFERENCE={reference_root}",
                          f"TORCH_INCLUDE={os.path.join(os.path.dirname(torch.__file__), 'include')}"],

@@ -65,7 +65,9 @@ DECODE_CASES = [
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MINFER_REFERENCE_ROOT")
+    if not root:
+        raise SystemExit("usage: make_golden.py /path/to/minfer-python   (or set MINFER_REFERENCE_ROOT)")
     refs = load_reference_refs(root)
     torch.set_num_threads(1)  # one summation order, whatever the host
 
