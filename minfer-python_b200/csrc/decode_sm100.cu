@@ -413,19 +413,63 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
   __syncthreads();
   if (!s_last) return;
   __threadfence();   // the other blocks' partials, written before their tickets, are visible now
-  for (int idx = tid; idx < a.group * D; idx += kWarps * 32) {
-    const int h = kvh * a.group + idx / D;
-    const int d = idx % D;
-    const size_t p0 = (static_cast<size_t>(b) * a.n_heads + h) * a.n_split;
-    float M = -INFINITY;
-    for (int s = 0; s < n_live; ++s) M = fmaxf(M, __ldcg(&a.part_ml[(p0 + s) * 2]));
-    float o = 0.f, l = 0.f;
-    for (int s = 0; s < n_live; ++s) {
-      const float sc = ex2_approx(__ldcg(&a.part_ml[(p0 + s) * 2]) - M);
-      l += sc * __ldcg(&a.part_ml[(p0 + s) * 2 + 1]);
-      o += sc * __ldcg(&a.part_o[(p0 + s) * D + d]);
+  // The merge sits at the very end of the sequence's work, so it is written for latency: the (max, sum)
+  // pairs of all splits are fetched in one round into shared memory, one thread per head turns them into
+  // per-split weights, and every output element then issues the loads of up to 16 splits at once.
+  constexpr int kMergeSplits = 256;  // splits whose weights fit the shared-memory table (more: slow path below)
+  float* w_tab = reinterpret_cast<float*>(smem);            // [group][n_live] weight of a split's partial
+  float* l_tab = w_tab + 16 * kMergeSplits;                 // [group][n_live] row sums, then [group] 1 / total
+  const size_t p_base = (static_cast<size_t>(b) * a.n_heads + static_cast<size_t>(kvh) * a.group) * a.n_split;
+  if (n_live <= kMergeSplits) {
+    for (int i = tid; i < a.group * n_live; i += kWarps * 32) {
+      const int g = i / n_live, sp = i % n_live;
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(&a.part_ml[(p_base + static_cast<size_t>(g) * a.n_split + sp) * 2]));
+      w_tab[g * n_live + sp] = ml.x;
+      l_tab[g * n_live + sp] = ml.y;
     }
-    const float r = (l > 0.f) ? o / l : 0.f;
+    __syncthreads();
+    if (tid < a.group) {
+      float M = -INFINITY;
+      for (int sp = 0; sp < n_live; ++sp) M = fmaxf(M, w_tab[tid * n_live + sp]);
+      float l = 0.f;
+      for (int sp = 0; sp < n_live; ++sp) {
+        const float sc = ex2_approx(w_tab[tid * n_live + sp] - M);
+        l += sc * l_tab[tid * n_live + sp];
+        w_tab[tid * n_live + sp] = sc;
+      }
+      l_tab[tid * n_live] = (l > 0.f) ? 1.f / l : 0.f;
+    }
+    __syncthreads();
+  }
+  for (int idx = tid; idx < a.group * D; idx += kWarps * 32) {
+    const int g = idx / D;
+    const int d = idx % D;
+    const float* po = a.part_o + (p_base + static_cast<size_t>(g) * a.n_split) * D + d;
+    float r;
+    if (n_live <= kMergeSplits) {
+      float o = 0.f;
+      for (int s0 = 0; s0 < n_live; s0 += 16) {
+        float x[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) x[j] = (s0 + j < n_live) ? __ldcg(po + static_cast<size_t>(s0 + j) * D) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (s0 + j < n_live) o += w_tab[g * n_live + s0 + j] * x[j];
+      }
+      r = o * l_tab[g * n_live];
+    } else {
+      const float* pm = a.part_ml + (p_base + static_cast<size_t>(g) * a.n_split) * 2;
+      float M = -INFINITY;
+      for (int sp = 0; sp < n_live; ++sp) M = fmaxf(M, __ldcg(pm + 2 * sp));
+      float o = 0.f, l = 0.f;
+      for (int sp = 0; sp < n_live; ++sp) {
+        const float sc = ex2_approx(__ldcg(pm + 2 * sp) - M);
+        l += sc * __ldcg(pm + 2 * sp + 1);
+        o += sc * __ldcg(po + static_cast<size_t>(sp) * D);
+      }
+      r = (l > 0.f) ? o / l : 0.f;
+    }
+    const int h = kvh * a.group + g;
     uint8_t* op = reinterpret_cast<uint8_t*>(a.out) +
                   2 * (static_cast<size_t>(b) * a.out_stride[0] + static_cast<size_t>(h) * a.out_stride[1] + d);
     if constexpr (BF16) *reinterpret_cast<__nv_bfloat16*>(op) = __float2bfloat16_rn(r);
@@ -438,6 +482,7 @@ cudaError_t launch_paged(const DecodeArgs& a, cudaStream_t stream) {
   constexpr int kRaw = Q8 ? kTileKeys * (D / 32) * 34 : kTileKeys * D * 2;
   constexpr int smem = kWarps * (kStages * 2 * kRaw + (Q8 ? kTileKeys * D * 2 : 0));
   static_assert(smem / kWarps >= 16 * D * 4 + 128, "the per-warp region also holds the fp32 merge buffer");
+  static_assert(smem >= 2 * 16 * 256 * 4, "the final merge keeps two [16][256] fp32 tables in shared memory");
   static bool attr_done[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);

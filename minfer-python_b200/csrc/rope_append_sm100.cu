@@ -23,8 +23,9 @@
 // The four threads that own one block's four chunks agree on the maximum with two shuffles.
 //
 // Thread mapping: a thread owns one token and one 16-byte chunk of head_dim
-// (neox: the chunk and its partner chunk) and loops over all heads, so the
-// sin/cos of its 4 (8) angles are computed once per token, not once per head.
+// (neox: the chunk and its partner chunk) and walks a slice of the token's rows
+// (query heads, k heads, v heads), four rows at a time with all loads issued
+// first; the sin/cos of its 4 (8) angles are computed once per thread.
 #include "../../include/minfer_attn.h"
 #include "attn_internal.h"
 
@@ -172,62 +173,107 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
     }
   }
 
-  // rotate chunk c (and its neox partner c2) of one head row into fp32; returns false if nothing changed
-  auto rot8f = [&](const uint8_t* src, const uint8_t* src2, float (&ox)[8], float (&oy)[8]) {
-    float x[8];
-    unpack8<BF16>(*reinterpret_cast<const uint4*>(src), x);
-    if (!rotate) {
-#pragma unroll
-      for (int t = 0; t < 8; ++t) ox[t] = x[t];
-      return;
-    }
-    if (kNeox) {
-      float y[8];
-      unpack8<BF16>(*reinterpret_cast<const uint4*>(src2), y);
-#pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        ox[t] = x[t] * cs[t] - y[t] * sn[t];
-        oy[t] = x[t] * sn[t] + y[t] * cs[t];
-      }
-    } else {
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        ox[2 * t] = x[2 * t] * cs[t] - x[2 * t + 1] * sn[t];
-        ox[2 * t + 1] = x[2 * t] * sn[t] + x[2 * t + 1] * cs[t];
-      }
-    }
-  };
-  auto rot8 = [&](const uint8_t* src, const uint8_t* src2, uint8_t* dst, uint8_t* dst2) {
-    float ox[8], oy[8];
-    rot8f(src, src2, ox, oy);
-    if (!rotate) {
-      if (dst != src) *reinterpret_cast<uint4*>(dst) = pack8<BF16>(ox);
-      return;
-    }
-    *reinterpret_cast<uint4*>(dst) = pack8<BF16>(ox);
-    if (kNeox) *reinterpret_cast<uint4*>(dst2) = pack8<BF16>(oy);
-  };
   const int q_row_bytes = (a.head_dim / 32) * 34;  // a Q8_0 cache row
 
   const size_t co = static_cast<size_t>(c) * 16, co2 = static_cast<size_t>(c2 < 0 ? 0 : c2) * 16;
-  // q: in place
-  if (a.q != nullptr && rotate) {
-    uint8_t* base = reinterpret_cast<uint8_t*>(a.q) + 2 * (static_cast<size_t>(b) * a.q_stride[0] + static_cast<size_t>(l) * a.q_stride[1]);
-    for (int h = 0; h < a.n_heads; ++h) {
-      uint8_t* row = base + 2 * static_cast<size_t>(h) * a.q_stride[2];
-      rot8(row + co, row + co2, row + co, row + co2);
+  // The rows of this token - its query heads, then its k heads, then its v heads - are dealt out over
+  // gridDim.y slices, and a thread takes its rows four at a time, all loads first: a thread that walked
+  // every head alone, one dependent load at a time, left the memory system idle (decode-sized calls took
+  // tens of microseconds, prefill-sized ones reached 0.64 of the copy bandwidth).
+  // The row list is the same for every thread of the launch (the threads that share a Q8_0 block must
+  // meet in the same row at the same step); what differs per thread is which kinds of row it has work for.
+  const bool do_q = rotate;
+  const bool do_k = to_cache ? cache_ok : rotate;
+  const bool do_v = cache_ok;
+  const int n_q = a.q != nullptr ? a.n_heads : 0;
+  const int n_k = a.k != nullptr ? a.n_kv_heads : 0;
+  const int n_rows = n_q + n_k + ((a.v != nullptr && a.v_cache != nullptr) ? a.n_kv_heads : 0);
+  const uint8_t* q_base = reinterpret_cast<const uint8_t*>(a.q) + 2 * (static_cast<size_t>(b) * a.q_stride[0] + static_cast<size_t>(l) * a.q_stride[1]);
+  const uint8_t* k_base = reinterpret_cast<const uint8_t*>(a.k) + 2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(l) * a.kv_stride[1]);
+  const uint8_t* v_base = reinterpret_cast<const uint8_t*>(a.v) + 2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(l) * a.kv_stride[1]);
+  // source row of combined row index r (kind 0 = q, 1 = k, 2 = v) and its head
+  auto row_of = [&](int r, int& kind, int& h) -> const uint8_t* {
+    if (r < n_q) {
+      kind = 0;
+      h = r;
+      return q_base + 2 * static_cast<size_t>(h) * a.q_stride[2];
     }
-  }
-  // k: rotated, into the cache (or in place when there is no cache)
-  if (a.k != nullptr && (to_cache ? cache_ok : rotate)) {
-    const uint8_t* base = reinterpret_cast<const uint8_t*>(a.k) + 2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(l) * a.kv_stride[1]);
-    for (int h = 0; h < a.n_kv_heads; ++h) {
-      const uint8_t* row = base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
-      if (a.cache_q8) {  // cache strides in bytes, rows contiguous
+    if (r < n_q + n_k) {
+      kind = 1;
+      h = r - n_q;
+      return k_base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
+    }
+    kind = 2;
+    h = r - n_q - n_k;
+    return v_base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
+  };
+  const int n_slices = static_cast<int>(gridDim.y);
+  for (int r0 = static_cast<int>(blockIdx.y); r0 < n_rows; r0 += 4 * n_slices) {
+    const uint8_t* src[4];
+    int kind[4], hh[4];
+    uint4 xa[4], xb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = r0 + j * n_slices;
+      kind[j] = -1;
+      if (r < n_rows) {
+        src[j] = row_of(r, kind[j], hh[j]);
+        if (!(kind[j] == 0 ? do_q : (kind[j] == 1 ? do_k : do_v))) kind[j] = -1;  // nothing to do for this row
+      }
+      if (kind[j] >= 0) {
+        xa[j] = *reinterpret_cast<const uint4*>(src[j] + co);
+        if (c2 >= 0) xb[j] = *reinterpret_cast<const uint4*>(src[j] + co2);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (kind[j] < 0) continue;
+      const int h = hh[j];
+      if (kind[j] == 2) {  // v: copied into the cache
+        if (a.cache_q8) {
+          uint8_t* qrow = reinterpret_cast<uint8_t*>(a.v_cache) + cb * a.cache_stride[0] +
+                          static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(crow) * q_row_bytes;
+          float x[8];
+          unpack8<BF16>(xa[j], x);
+          store_q8_quarter(x, qrow + (c >> 2) * 34, c & 3);
+          if (c2 >= 0) {
+            unpack8<BF16>(xb[j], x);
+            store_q8_quarter(x, qrow + (c2 >> 2) * 34, c2 & 3);
+          }
+        } else {
+          uint8_t* drow = reinterpret_cast<uint8_t*>(a.v_cache) + 2 * (cb * a.cache_stride[0] + static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(crow) * a.cache_stride[2]);
+          *reinterpret_cast<uint4*>(drow + co) = xa[j];
+          if (c2 >= 0) *reinterpret_cast<uint4*>(drow + co2) = xb[j];
+        }
+        continue;
+      }
+      // q and k: rotate
+      float ox[8], oy[8];
+      {
+        float x[8];
+        unpack8<BF16>(xa[j], x);
+        if (!rotate) {
+#pragma unroll
+          for (int t = 0; t < 8; ++t) ox[t] = x[t];
+        } else if (kNeox) {
+          float y[8];
+          unpack8<BF16>(xb[j], y);
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            ox[t] = x[t] * cs[t] - y[t] * sn[t];
+            oy[t] = x[t] * sn[t] + y[t] * cs[t];
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            ox[2 * t] = x[2 * t] * cs[t] - x[2 * t + 1] * sn[t];
+            ox[2 * t + 1] = x[2 * t] * sn[t] + x[2 * t + 1] * cs[t];
+          }
+        }
+      }
+      if (kind[j] == 1 && a.cache_q8) {  // k into a Q8_0 cache (strides in bytes, rows contiguous)
         uint8_t* qrow = reinterpret_cast<uint8_t*>(a.k_cache) + cb * a.cache_stride[0] +
                         static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(crow) * q_row_bytes;
-        float ox[8], oy[8];
-        rot8f(row + co, row + co2, ox, oy);
         round16<BF16>(ox);
         store_q8_quarter(ox, qrow + (c >> 2) * 34, c & 3);
         if (c2 >= 0) {
@@ -236,32 +282,12 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
         }
         continue;
       }
-      uint8_t* drow = a.k_cache != nullptr
+      // q in place; k into the 16-bit cache, or in place when the call has no cache
+      uint8_t* drow = (kind[j] == 1 && a.k_cache != nullptr)
                           ? reinterpret_cast<uint8_t*>(a.k_cache) + 2 * (cb * a.cache_stride[0] + static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(crow) * a.cache_stride[2])
-                          : const_cast<uint8_t*>(row);
-      rot8(row + co, row + co2, drow + co, drow + co2);
-    }
-  }
-  // v: copied into the cache
-  if (a.v != nullptr && a.v_cache != nullptr && cache_ok) {
-    const uint8_t* base = reinterpret_cast<const uint8_t*>(a.v) + 2 * (static_cast<size_t>(b) * a.kv_stride[0] + static_cast<size_t>(l) * a.kv_stride[1]);
-    for (int h = 0; h < a.n_kv_heads; ++h) {
-      const uint8_t* row = base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
-      if (a.cache_q8) {
-        uint8_t* qrow = reinterpret_cast<uint8_t*>(a.v_cache) + cb * a.cache_stride[0] +
-                        static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(crow) * q_row_bytes;
-        float x[8];
-        unpack8<BF16>(*reinterpret_cast<const uint4*>(row + co), x);
-        store_q8_quarter(x, qrow + (c >> 2) * 34, c & 3);
-        if (c2 >= 0) {
-          unpack8<BF16>(*reinterpret_cast<const uint4*>(row + co2), x);
-          store_q8_quarter(x, qrow + (c2 >> 2) * 34, c2 & 3);
-        }
-        continue;
-      }
-      uint8_t* drow = reinterpret_cast<uint8_t*>(a.v_cache) + 2 * (cb * a.cache_stride[0] + static_cast<size_t>(h) * a.cache_stride[1] + static_cast<size_t>(crow) * a.cache_stride[2]);
-      *reinterpret_cast<uint4*>(drow + co) = *reinterpret_cast<const uint4*>(row + co);
-      if (c2 >= 0) *reinterpret_cast<uint4*>(drow + co2) = *reinterpret_cast<const uint4*>(row + co2);
+                          : const_cast<uint8_t*>(src[j]);
+      if (rotate || drow != src[j]) *reinterpret_cast<uint4*>(drow + co) = pack8<BF16>(ox);
+      if (rotate && kNeox) *reinterpret_cast<uint4*>(drow + co2) = pack8<BF16>(oy);
     }
   }
 }
@@ -272,7 +298,16 @@ cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, bool neox, cudaStre
   const int chunks = a.head_dim / 8;
   const int work_chunks = neox ? chunks - a.rotary_dim / 16 : chunks;
   const long long threads = static_cast<long long>(a.batch) * a.seq * work_chunks;
-  const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+  // Slices over the token's rows (query heads + k heads + v heads): enough of them that about 128 k threads are
+  // in flight, but no fewer than four rows per thread where there is that much work (every thread computes the
+  // sines and cosines of its chunk's angles once, whatever its number of rows)
+  const int n_rows = (a.q != nullptr ? a.n_heads : 0) + (a.k != nullptr ? a.n_kv_heads : 0) +
+                     (a.v != nullptr && a.v_cache != nullptr ? a.n_kv_heads : 0);
+  long long slices = (131072 + threads - 1) / threads;
+  const long long max_slices = threads >= 65536 ? (n_rows + 3) / 4 : n_rows;
+  if (slices > max_slices) slices = max_slices;
+  if (slices < 1) slices = 1;
+  const dim3 grid(static_cast<unsigned>((threads + 255) / 256), static_cast<unsigned>(slices));
   if (bf16) {
     if (neox) rope_append_kernel<true, true><<<grid, 256, 0, stream>>>(a);
     else rope_append_kernel<true, false><<<grid, 256, 0, stream>>>(a);

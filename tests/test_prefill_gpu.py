@@ -287,8 +287,13 @@ def test_bf16_medium(kerns, record_property):
     print("bf16 L=1024:", counts)
     record_property("bf16_counts", counts)
     check_close(got, want, "bf16", bf16=True)
-    # whatever fails the plain tolerance is explained by the output type, not by the arithmetic
-    assert counts["fail_plain_2e-3"] <= 4 * max(1, counts["rounded_oracle_fails_plain"])
+    # The elements outside the plain tolerance sit where one bfloat16 step (0.0156 for |x| in [2, 4)) exceeds
+    # the tolerance itself: a result that lands on the neighbouring bfloat16 value is off by up to a step
+    # minus the oracle's own rounding distance.  They must be rare and confined to such magnitudes.
+    a, e = got.float().cpu(), want.float()
+    bad = (a - e).abs() > 2e-3 + 2e-3 * e.abs()
+    assert counts["fail_plain_2e-3"] <= 1e-4 * counts["elements"]
+    assert not bad.any() or float(e[bad].abs().min()) >= 1.0
 
 
 def test_config4_long_context_bf16_shard_and_full(kerns, record_property):
