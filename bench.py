@@ -616,6 +616,52 @@ def extra_legs(kerns, args, dev, peaks):
     return legs
 
 
+HOST_OVERHEAD_SCRIPT = r"""
+import sys, time, json, torch
+sys.path.insert(0, {pkg!r})
+from minfer.kernels import KernelBackend
+from minfer.kernels.torch_ext import ops
+kerns = KernelBackend("torch_ext")
+dev = torch.device("cuda", 0)
+q = torch.randn(1, 4, 128, 128, device=dev, dtype=torch.float16); k = torch.randn(1, 2, 128, 128, device=dev, dtype=torch.float16)
+v = torch.randn_like(k); out = torch.zeros_like(q)
+mask = torch.ones(1, 1, 128, 128, dtype=torch.bool, device=dev)
+dq = torch.randn(4, 8, 1, 128, device=dev, dtype=torch.float16); kc = torch.randn(4, 2, 256, 128, device=dev, dtype=torch.float16)
+vc = torch.randn_like(kc); lens = torch.full((4,), 200, dtype=torch.int32, device=dev); dout = torch.zeros_like(dq)
+calls = {{"flash_attn_causal": lambda: kerns.flash_attn_causal(q, k, v, out),
+          "flash_attn": lambda: kerns.flash_attn(1, 1, 2, q, k, v, mask, out),
+          "flash_attn_decode": lambda: kerns.flash_attn_decode(dq, kc, vc, lens, dout)}}
+res = {{"binding": ops.BINDING}}
+for name, fn in calls.items():
+    for _ in range(200): fn()
+    torch.cuda.synchronize()
+    total, n = 0.0, 0
+    for _ in range(20):                      # 20 x 500 = 10 k calls; the device is drained between batches, untimed
+        t0 = time.perf_counter()
+        for _ in range(500): fn()
+        total += time.perf_counter() - t0; n += 500
+        torch.cuda.synchronize()
+    res[name] = total / n * 1e6
+print(json.dumps(res))
+"""
+
+
+def host_overhead_record():
+    """CPU-side cost of one op call (microseconds, 10 k calls on tiny shapes so that the device never back-pressures
+    the host), for the torch-extension binding and for the ctypes binding, each in a process of its own."""
+    out = {}
+    for binding in ("stable", "ctypes"):
+        env = dict(os.environ, MINFER_ATTN_BINDING=binding)
+        script = HOST_OVERHEAD_SCRIPT.format(pkg=os.path.join(ROOT, "minfer-python_b200"))
+        try:
+            r = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=300)
+            out[binding] = json.loads(r.stdout.strip().splitlines()[-1]) if r.returncode == 0 else {"error": (r.stderr or "")[-200:]}
+        except Exception as e:  # noqa: BLE001  (a missing extension must not take the benchmark down)
+            out[binding] = {"error": repr(e)[:200]}
+    out["unit"] = "microseconds of host time per call"
+    return out
+
+
 def config5_record(dev):
     """apps/generate.py at the Llama-3.2-1B shape: 8 prompts x 512 tokens, 128 greedy steps."""
     import importlib.util
@@ -668,6 +714,7 @@ def run_gpu_arm(args):
     legs = c5 = None
     if world == 1 and args.legs == "all":
         legs = extra_legs(kerns, args, dev, peaks)
+        legs["host_overhead"] = host_overhead_record()
         c5 = config5_record(dev)
 
     if rank == 0:

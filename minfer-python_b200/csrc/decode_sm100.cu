@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
   __threadfence();   // the other blocks' partials, written before their tickets, are visible now
   // The merge sits at the very end of the sequence's work, so it is written for latency: the (max, sum)
   // pairs of all splits are fetched in one round into shared memory, one thread per head turns them into
-  // per-split weights, and every output element then issues the loads of up to 16 splits at once.
+  // per-split weights, and every output element then issues the loads of eight splits at a time.
   constexpr int kMergeSplits = 256;  // splits whose weights fit the shared-memory table (more: slow path below)
   float* w_tab = reinterpret_cast<float*>(smem);            // [group][n_live] weight of a split's partial
   float* l_tab = w_tab + 16 * kMergeSplits;                 // [group][n_live] row sums, then [group] 1 / total
@@ -448,12 +448,13 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
     float r;
     if (n_live <= kMergeSplits) {
       float o = 0.f;
-      for (int s0 = 0; s0 < n_live; s0 += 16) {
-        float x[16];
+      constexpr int kBatch = 8;  // loads in flight per output element
+      for (int s0 = 0; s0 < n_live; s0 += kBatch) {
+        float x[kBatch];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) x[j] = (s0 + j < n_live) ? __ldcg(po + static_cast<size_t>(s0 + j) * D) : 0.f;
+        for (int j = 0; j < kBatch; ++j) x[j] = (s0 + j < n_live) ? __ldcg(po + static_cast<size_t>(s0 + j) * D) : 0.f;
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
+        for (int j = 0; j < kBatch; ++j)
           if (s0 + j < n_live) o += w_tab[g * n_live + s0 + j] * x[j];
       }
       r = o * l_tab[g * n_live];
