@@ -451,8 +451,8 @@ def decode_leg(kerns, args, rank, world, dev, peaks, traffic):
     return rec, extra
 
 
-DECODE_LAUNCHES = 1
-DECODE_KERNELS = "decode_split_kernel<128,f16> (the last thread block of a sequence and kv head merges its splits)"
+DECODE_LAUNCHES = 2
+DECODE_KERNELS = "decode_split_kernel<128,f16> + decode_combine_kernel"
 
 
 def config4_record(kerns, args, rank, world, dev, peaks):
@@ -582,7 +582,7 @@ def extra_legs(kerns, args, dev, peaks):
     ms = time_gpu(lambda: kerns.flash_attn_decode_q8(dq, kq, vq, dl, dout), 200, 5, 1, dev)
     q8_bytes = 2.0 * Hk * row * float(lens.sum())
     legs["decode_q8_0"] = {"ms": ms, "bytes_per_step": q8_bytes, "tokens_per_s_equivalent_16bit_gbs": 2.0 * 2 * Hk * Dd * float(lens.sum()) / (ms * 1e-3) / 1e9,
-                           "roofline": hbm_roof(q8_bytes / (ms * 1e-3) / 1e9, "decode_split_kernel<128,f16,q8>")}
+                           "roofline": hbm_roof(q8_bytes / (ms * 1e-3) / 1e9, "decode_split_kernel<128,f16,q8> + decode_combine_kernel")}
     del kq, vq
     page = 64
     pages_per_seq = Lm // page
@@ -593,7 +593,7 @@ def extra_legs(kerns, args, dev, peaks):
     ms = time_gpu(lambda: kerns.flash_attn_decode_paged(dq, kp, vp, table, dl, dout), 200, 5, 1, dev)
     fp_bytes = 2.0 * 2 * Hk * Dd * float(lens.sum())
     legs["decode_paged_64"] = {"ms": ms, "bytes_per_step": fp_bytes, "page_size": page, "page_order": "shuffled",
-                               "roofline": hbm_roof(fp_bytes / (ms * 1e-3) / 1e9, "decode_split_kernel<128,f16,paged>")}
+                               "roofline": hbm_roof(fp_bytes / (ms * 1e-3) / 1e9, "decode_split_kernel<128,f16,paged> + decode_combine_kernel")}
     del kp, vp, table
     torch.cuda.empty_cache()
 

@@ -139,11 +139,10 @@ size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t
  * sequence with lens[b] == 0 yields zeros.
  *
  * The KV range of a sequence is cut into chunks of `chunk` keys, each handled
- * by its own thread block (split-KV); partial results and one arrival counter
- * per (sequence, kv head) go through `workspace`, a device buffer of at least
- * minfer_attn_decode_workspace_bytes() bytes that the caller owns (any content;
- * the call clears the counters on `stream`).  The thread block that arrives last
- * for a (sequence, kv head) merges its splits and writes `out`: one launch.  chunk == 0 lets the library choose; otherwise it must be a
+ * by its own thread block (split-KV); partial results go through `workspace`,
+ * a device buffer of at least minfer_attn_decode_workspace_bytes() bytes that
+ * the caller owns (any content); a second, small kernel merges the splits of
+ * every sequence and writes `out`.  chunk == 0 lets the library choose; otherwise it must be a
  * positive multiple of 64.
  *
  * kv_format == MINFER_ATTN_KV_Q8_0: the caches hold GGML Q8_0 blocks (the
@@ -225,11 +224,9 @@ int32_t minfer_attn_decode_default_chunk(int32_t batch, int32_t n_kv_heads,
  *     the array and the call then fails with MINFER_ATTN_ECUDA
  *     (minfer_attn_last_cuda_error() names the cause).
  *   - All calls on a device share the one array, which keeps the last call's
- *     contents.  The only part that has to start at zero, the arrival counters,
- *     is cleared by every call on `stream` before its kernel (every partial that
- *     is read was written earlier in the same call).  Two calls whose kernels
- *     overlap on the GPU race on the array: issue them on one stream, or order
- *     them with events.
+ *     contents.  Nothing in it has to start at zero (every partial that is read
+ *     was written earlier in the same call), but two calls whose kernels overlap
+ *     on the GPU race on it: issue them on one stream, or order them with events.
  *   - The function calls neither cudaMalloc/cudaFree nor any allocating
  *     library routine.
  * This entry point has no counterpart in the reference.

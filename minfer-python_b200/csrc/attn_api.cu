@@ -328,10 +328,7 @@ size_t minfer_attn_decode_workspace_bytes(int32_t batch, int32_t n_heads, int32_
   if (chunk == 0) chunk = default_chunk(batch, 1, max_len);
   if (chunk < 64 || chunk % 64 != 0) return 0;
   const size_t n_split = (static_cast<size_t>(max_len) + chunk - 1) / chunk;
-  // fp32 partials (output, then max and sum) and one arrival counter per (sequence, kv head) - sized by
-  // n_heads, which bounds n_kv_heads
-  return static_cast<size_t>(batch) * n_heads * n_split * (static_cast<size_t>(head_dim) + 2) * sizeof(float) +
-         static_cast<size_t>(batch) * n_heads * sizeof(int);
+  return static_cast<size_t>(batch) * n_heads * n_split * (static_cast<size_t>(head_dim) + 2) * sizeof(float);
 }
 
 int minfer_attn_decode(const MinferAttnDecodeParams* p, void* stream) {
@@ -390,7 +387,6 @@ int minfer_attn_decode(const MinferAttnDecodeParams* p, void* stream) {
   a.n_split = (p->max_len + chunk - 1) / chunk;
   a.part_o = static_cast<float*>(p->workspace);
   a.part_ml = a.part_o + static_cast<size_t>(p->batch) * p->n_heads * a.n_split * p->head_dim;
-  a.tickets = reinterpret_cast<int*>(a.part_ml + static_cast<size_t>(p->batch) * p->n_heads * a.n_split * 2);
   for (int i = 0; i < 2; ++i) {
     a.q_stride[i] = p->q_stride[i];
     a.out_stride[i] = p->out_stride[i];

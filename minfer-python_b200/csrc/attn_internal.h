@@ -80,7 +80,6 @@ struct DecodeArgs {
   void* out;
   float* part_o;   // [batch, n_heads, n_split, head_dim] fp32, unnormalised
   float* part_ml;  // [batch, n_heads, n_split, 2] running max (log2 domain) and sum
-  int* tickets;    // [batch, n_kv_heads] arrival counters of the splits (zero between calls)
   int64_t q_stride[2];
   int64_t kv_stride[3];   // elements; for a Q8_0 cache: bytes (batch, head), rows contiguous
   int64_t out_stride[2];

@@ -14,10 +14,6 @@
 // 16 rows of m16n8k16 tensor-core tiles so the arithmetic stays far below the
 // memory time.  The warps' states are merged through shared memory and written
 // as one fp32 partial (max, sum, unnormalised output) per (query head, split).
-// The thread blocks of one (sequence, kv head) then take a ticket from a counter
-// in the workspace; whoever draws the last one merges the partials of all splits
-// (in split order, so the result does not depend on who that is) and writes the
-// 16-bit output.  Nobody waits for anybody: one launch, no second kernel.
 //
 // Q8 = true: the caches hold GGML Q8_0 blocks (32 int8 + one fp16 scale, 34 bytes;
 // the reference's block_q8_0, src/minfer/kernels/torch_ext/csrc/common/types.hpp:141-146).
@@ -27,6 +23,12 @@
 // does ((half)(q * d), csrc/quants/impl.cpp:1153-1166), and the arithmetic above
 // runs unchanged.  Cache bytes per key drop from 4 D to 2.125 D.
 //
+// Kernel 2 (decode_combine_kernel): grid (n_heads, batch) merges the partials
+// of the ceil(len / chunk) splits of a sequence and writes the 16-bit output.
+// (A one-launch form - every thread block takes a ticket from a counter after
+// writing its partial and the last one of a (sequence, kv head) merges - was
+// built and measured: the fence and the atomic add about 2 us to every 12 us
+// thread block, which costs more than this second launch does.)
 #include "attn_internal.h"
 #include "ptx.cuh"
 
@@ -40,6 +42,15 @@ namespace {
 constexpr int kWarps = 4;
 constexpr int kStages = 3;
 constexpr int kTileKeys = 16;
+
+// kept out of line: the error path must not cost the streaming loop registers
+__device__ __noinline__ void report_bad_page(int32_t* status, int b, int slot, int page) {
+  if (status != nullptr && atomicCAS(status, 0, kStatusBadPage) == 0) {
+    status[1] = b;
+    status[2] = slot;
+    status[3] = page;
+  }
+}
 
 template <int D>
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
@@ -124,16 +135,6 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
 
   const int len = min(a.lens[b], a.max_len);
   const int c0 = split * a.chunk;
-  if (len <= 0 && split == 0) {
-    // an empty sequence has no split to merge: its output rows are zeros
-    for (int idx = tid; idx < a.group * D; idx += kWarps * 32) {
-      const int h = kvh * a.group + idx / D;
-      uint8_t* op = reinterpret_cast<uint8_t*>(a.out) +
-                    2 * (static_cast<size_t>(b) * a.out_stride[0] + static_cast<size_t>(h) * a.out_stride[1] + idx % D);
-      *reinterpret_cast<uint16_t*>(op) = 0;
-    }
-    return;
-  }
   if (c0 >= len) return;
   const int c1 = min(len, c0 + a.chunk);
   const int nt = (c1 - c0 + kTileKeys - 1) / kTileKeys;
@@ -153,11 +154,7 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
       int page = __ldg(a.block_table + static_cast<size_t>(b) * a.table_stride + slot);
       if (static_cast<unsigned>(page) >= static_cast<unsigned>(a.n_pages)) {
         // never follow an entry that points outside the pools: report it and read page 0 instead
-        if (lane == 0 && a.status != nullptr && atomicCAS(a.status, 0, kStatusBadPage) == 0) {
-          a.status[1] = b;
-          a.status[2] = slot;
-          a.status[3] = page;
-        }
+        if (lane == 0) report_bad_page(a.status, b, slot, page);
         page = 0;
       }
       return kUnit * static_cast<size_t>(page) * a.kv_stride[0] + head_off + static_cast<size_t>(key0 % a.page_size) * row_bytes;
@@ -398,84 +395,29 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
       a.part_ml[pidx * 2 + 1] = l;
     }
   }
+}
 
-  // ---- ticket: the last thread block of this (sequence, kv head) merges the splits ----
-  const int n_live = (len + a.chunk - 1) / a.chunk;
-  __shared__ int s_last;
-  __threadfence();   // this block's partials are visible device-wide before its ticket is
-  __syncthreads();
-  if (tid == 0) {
-    int* ticket = a.tickets + static_cast<size_t>(b) * a.n_kv_heads + kvh;
-    const int t = atomicAdd(ticket, 1);
-    s_last = (t == n_live - 1) ? 1 : 0;
-    if (s_last) *ticket = 0;  // left as found: zero
+template <int D, bool BF16>
+__global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
+  const int h = blockIdx.x;
+  const int b = blockIdx.y;
+  const int d = threadIdx.x;
+  const int len = min(a.lens[b], a.max_len);
+  const int ns = (len + a.chunk - 1) / a.chunk;
+  const size_t p0 = (static_cast<size_t>(b) * a.n_heads + h) * a.n_split;
+  float M = -INFINITY;
+  for (int s = 0; s < ns; ++s) M = fmaxf(M, a.part_ml[(p0 + s) * 2]);
+  float o = 0.f, l = 0.f;
+  for (int s = 0; s < ns; ++s) {
+    const float sc = ex2_approx(a.part_ml[(p0 + s) * 2] - M);
+    l += sc * a.part_ml[(p0 + s) * 2 + 1];
+    o += sc * a.part_o[(p0 + s) * D + d];
   }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();   // the other blocks' partials, written before their tickets, are visible now
-  // The merge sits at the very end of the sequence's work, so it is written for latency: the (max, sum)
-  // pairs of all splits are fetched in one round into shared memory, one thread per head turns them into
-  // per-split weights, and every output element then issues the loads of eight splits at a time.
-  constexpr int kMergeSplits = 256;  // splits whose weights fit the shared-memory table (more: slow path below)
-  float* w_tab = reinterpret_cast<float*>(smem);            // [group][n_live] weight of a split's partial
-  float* l_tab = w_tab + 16 * kMergeSplits;                 // [group][n_live] row sums, then [group] 1 / total
-  const size_t p_base = (static_cast<size_t>(b) * a.n_heads + static_cast<size_t>(kvh) * a.group) * a.n_split;
-  if (n_live <= kMergeSplits) {
-    for (int i = tid; i < a.group * n_live; i += kWarps * 32) {
-      const int g = i / n_live, sp = i % n_live;
-      const float2 ml = __ldcg(reinterpret_cast<const float2*>(&a.part_ml[(p_base + static_cast<size_t>(g) * a.n_split + sp) * 2]));
-      w_tab[g * n_live + sp] = ml.x;
-      l_tab[g * n_live + sp] = ml.y;
-    }
-    __syncthreads();
-    if (tid < a.group) {
-      float M = -INFINITY;
-      for (int sp = 0; sp < n_live; ++sp) M = fmaxf(M, w_tab[tid * n_live + sp]);
-      float l = 0.f;
-      for (int sp = 0; sp < n_live; ++sp) {
-        const float sc = ex2_approx(w_tab[tid * n_live + sp] - M);
-        l += sc * l_tab[tid * n_live + sp];
-        w_tab[tid * n_live + sp] = sc;
-      }
-      l_tab[tid * n_live] = (l > 0.f) ? 1.f / l : 0.f;
-    }
-    __syncthreads();
-  }
-  for (int idx = tid; idx < a.group * D; idx += kWarps * 32) {
-    const int g = idx / D;
-    const int d = idx % D;
-    const float* po = a.part_o + (p_base + static_cast<size_t>(g) * a.n_split) * D + d;
-    float r;
-    if (n_live <= kMergeSplits) {
-      float o = 0.f;
-      constexpr int kBatch = 8;  // loads in flight per output element
-      for (int s0 = 0; s0 < n_live; s0 += kBatch) {
-        float x[kBatch];
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) x[j] = (s0 + j < n_live) ? __ldcg(po + static_cast<size_t>(s0 + j) * D) : 0.f;
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j)
-          if (s0 + j < n_live) o += w_tab[g * n_live + s0 + j] * x[j];
-      }
-      r = o * l_tab[g * n_live];
-    } else {
-      const float* pm = a.part_ml + (p_base + static_cast<size_t>(g) * a.n_split) * 2;
-      float M = -INFINITY;
-      for (int sp = 0; sp < n_live; ++sp) M = fmaxf(M, __ldcg(pm + 2 * sp));
-      float o = 0.f, l = 0.f;
-      for (int sp = 0; sp < n_live; ++sp) {
-        const float sc = ex2_approx(__ldcg(pm + 2 * sp) - M);
-        l += sc * __ldcg(pm + 2 * sp + 1);
-        o += sc * __ldcg(po + static_cast<size_t>(sp) * D);
-      }
-      r = (l > 0.f) ? o / l : 0.f;
-    }
-    const int h = kvh * a.group + g;
-    uint8_t* op = reinterpret_cast<uint8_t*>(a.out) +
-                  2 * (static_cast<size_t>(b) * a.out_stride[0] + static_cast<size_t>(h) * a.out_stride[1] + d);
-    if constexpr (BF16) *reinterpret_cast<__nv_bfloat16*>(op) = __float2bfloat16_rn(r);
-    else *reinterpret_cast<__half*>(op) = __float2half_rn(r);
-  }
+  const float r = (l > 0.f) ? o / l : 0.f;
+  uint8_t* op = reinterpret_cast<uint8_t*>(a.out) +
+                2 * (static_cast<size_t>(b) * a.out_stride[0] + static_cast<size_t>(h) * a.out_stride[1] + d);
+  if constexpr (BF16) *reinterpret_cast<__nv_bfloat16*>(op) = __float2bfloat16_rn(r);
+  else *reinterpret_cast<__half*>(op) = __float2half_rn(r);
 }
 
 template <int D, bool BF16, bool Q8, bool Paged>
@@ -483,7 +425,6 @@ cudaError_t launch_paged(const DecodeArgs& a, cudaStream_t stream) {
   constexpr int kRaw = Q8 ? kTileKeys * (D / 32) * 34 : kTileKeys * D * 2;
   constexpr int smem = kWarps * (kStages * 2 * kRaw + (Q8 ? kTileKeys * D * 2 : 0));
   static_assert(smem / kWarps >= 16 * D * 4 + 128, "the per-warp region also holds the fp32 merge buffer");
-  static_assert(smem >= 2 * 16 * 256 * 4, "the final merge keeps two [16][256] fp32 tables in shared memory");
   static bool attr_done[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -493,12 +434,11 @@ cudaError_t launch_paged(const DecodeArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
-  // the ticket counters start at zero (the kernel also leaves them at zero, but the workspace is the
-  // caller's and may hold anything on first use)
-  e = cudaMemsetAsync(a.tickets, 0, sizeof(int) * static_cast<size_t>(a.batch) * a.n_kv_heads, stream);
-  if (e != cudaSuccess) return e;
   dim3 grid(a.n_split, a.n_kv_heads, a.batch);
   decode_split_kernel<D, BF16, Q8, Paged><<<grid, kWarps * 32, smem, stream>>>(a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  decode_combine_kernel<D, BF16><<<dim3(a.n_heads, a.batch), D, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

@@ -253,8 +253,11 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   constexpr int kKvEmpty = kKvFull + kStages;
   constexpr int kNumBars = kKvFull + 2 * kStages;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kIdescS = umma_idesc(kTileM, kTileN, BF16, false, false);
-  constexpr uint32_t kIdescO = umma_idesc(kTileM, D, BF16, false, true);
+  constexpr uint32_t kIdescS = umma_idesc(kTileM, kTileN, BF16, BF16, false, false);
+  // P is always float16, whatever the type of q/k/v: its values lie in (0, 2^8] (the lazy rescale bounds them), where
+  // float16 resolves 2^-11 against bfloat16's 2^-8 - with a bfloat16 P the rounding of the weights alone reached
+  // the tolerance on rows that average only a few keys.  The PV MMA therefore takes a float16 A and V's type as B.
+  constexpr uint32_t kIdescO = umma_idesc(kTileM, D, false, BF16, false, true);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -819,7 +822,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
               p.y = ex2_approx(x.y);
             }
             sum2 = __fadd2_rn(sum2, p);
-            pk[e] = pack2<BF16>(p.x, p.y);
+            pk[e] = pack2<false>(p.x, p.y);
           }
           tmem_st16(tmem_p + c * 16, pk);
           if (c == 3 || c + 1 == kPSplit) {

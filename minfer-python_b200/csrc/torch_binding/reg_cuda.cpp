@@ -88,6 +88,17 @@ void check_rc(int rc, const char* what) {
   STD_TORCH_CHECK(false, msg);
 }
 
+// GGML Q8_0 cache: uint8 [B, Hkv, Lmax, head_dim / 32 * 34], rows of one head contiguous
+void check_q8_cache(const Tensor& cache, int64_t batch, int64_t head_dim, const char* what) {
+  STD_TORCH_CHECK(cache.is_cuda() && cache.scalar_type() == ScalarType::Byte && cache.dim() == 4,
+                  std::string(what) + " must be a CUDA uint8 [B, Hkv, Lmax, bytes] tensor");
+  STD_TORCH_CHECK(cache.size(0) == batch && cache.size(3) == head_dim / 32 * 34,
+                  std::string(what) + ": batch or row bytes do not match (row = head_dim/32 blocks of 34 bytes)");
+  STD_TORCH_CHECK(cache.stride(3) == 1 && cache.stride(2) == cache.size(3), std::string(what) + ": rows of one head must be contiguous");
+  // rows of one (batch, head) must end on a 16-byte boundary
+  STD_TORCH_CHECK(cache.size(2) % (head_dim == 64 ? 4 : 2) == 0, std::string(what) + ": the padded length must be a multiple of 2 (4 for head_dim 64)");
+}
+
 void check_qkv(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out) {
   STD_TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda() && out.is_cuda(), "all tensors must be on CUDA");
   STD_TORCH_CHECK(q.get_device_index() == k.get_device_index() && q.get_device_index() == v.get_device_index() &&
@@ -228,6 +239,123 @@ void flash_attn_decode_paged_cuda(const Tensor& q, const Tensor& k_pages, const 
   decode(q, k_pages, v_pages, &block_table, lens, out, MINFER_ATTN_KV_16BIT);
 }
 
+void flash_attn_decode_q8_cuda(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& lens, Tensor& out) {
+  STD_TORCH_CHECK(q.is_cuda() && out.is_cuda() && q.dim() == 4 && out.dim() == 4 && q.sizes().equals(out.sizes()),
+                  "q/out must be CUDA [B, H, 1, D] tensors");
+  STD_TORCH_CHECK(q.scalar_type() == out.scalar_type() && q.stride(-1) == 1 && out.stride(-1) == 1, "q/out dtype or innermost stride");
+  check_q8_cache(k_cache, q.size(0), q.size(3), "k_cache");
+  check_q8_cache(v_cache, q.size(0), q.size(3), "v_cache");
+  STD_TORCH_CHECK(k_cache.sizes().equals(v_cache.sizes()) && k_cache.strides().equals(v_cache.strides()),
+                  "the caches must share shape and strides");
+  STD_TORCH_CHECK(q.size(1) % k_cache.size(1) == 0, "n_heads must be a multiple of n_kv_heads");
+  decode(q, k_cache, v_cache, nullptr, lens, out, MINFER_ATTN_KV_Q8_0);
+}
+
+// ---- rotary embedding (+ KV-cache append): minfer_attn_rope_append ----
+void rope_in_place(int style, int64_t rotary_dim, int64_t start_pos, double freq_base, Tensor& x) {
+  // the checks of the reference's launcher (csrc/cuda/il_rope/op.cuh:27-31), bfloat16 admitted
+  STD_TORCH_CHECK(x.is_cuda(), "x must be on CUDA");
+  STD_TORCH_CHECK(x.is_contiguous(), "x must be contiguous");
+  STD_TORCH_CHECK(x.dim() == 4, "x must be [B, L, n_heads, head_dim]");
+  STD_TORCH_CHECK(rotary_dim <= x.size(3), "rotary_dim exceeds head_dim");
+  MinferRopeParams p{};
+  p.q = x.mutable_data_ptr();
+  for (int i = 0; i < 3; ++i) p.q_stride[i] = x.stride(i);
+  p.batch = static_cast<int32_t>(x.size(0));
+  p.seq = static_cast<int32_t>(x.size(1));
+  p.n_heads = static_cast<int32_t>(x.size(2));
+  p.head_dim = static_cast<int32_t>(x.size(3));
+  p.rotary_dim = static_cast<int32_t>(rotary_dim);
+  p.start_pos = static_cast<int32_t>(start_pos);
+  p.freq_base = static_cast<float>(freq_base);
+  p.dtype = dtype_tag(x);
+  p.style = style;
+  check_rc(minfer_attn_rope_append(&p, current_stream()), "minfer_attn_rope_append");
+}
+
+void il_rope_cuda(int64_t rotary_dim, int64_t start_pos, double freq_base, Tensor& x) {
+  rope_in_place(0, rotary_dim, start_pos, freq_base, x);
+}
+
+void neox_rope_cuda(int64_t rotary_dim, int64_t start_pos, double freq_base, Tensor& x) {
+  rope_in_place(1, rotary_dim, start_pos, freq_base, x);
+}
+
+void rope_append(int64_t rotary_dim, double freq_base, int64_t style, Tensor& q, const Tensor& k, const Tensor& v,
+                 Tensor& k_cache, Tensor& v_cache, const Tensor* table, const Tensor& start, bool q8) {
+  STD_TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda() && k_cache.is_cuda() && v_cache.is_cuda() && start.is_cuda(),
+                  "all tensors must be on CUDA");
+  STD_TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4 && k_cache.dim() == 4 && v_cache.dim() == 4,
+                  "q/k/v must be [B, L, H, D] and the caches [B, Hkv, Lmax, D]");
+  if (q8) {
+    STD_TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type(), "dtypes differ");
+    check_q8_cache(k_cache, q.size(0), q.size(3), "k_cache");
+    check_q8_cache(v_cache, q.size(0), q.size(3), "v_cache");
+  } else {
+    STD_TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type() &&
+                    q.scalar_type() == k_cache.scalar_type() && q.scalar_type() == v_cache.scalar_type(), "dtypes differ");
+  }
+  STD_TORCH_CHECK(k.sizes().equals(v.sizes()) && k.strides().equals(v.strides()), "k and v must share shape and strides");
+  STD_TORCH_CHECK(k_cache.sizes().equals(v_cache.sizes()) && k_cache.strides().equals(v_cache.strides()),
+                  "the caches must share shape and strides");
+  STD_TORCH_CHECK(q.size(0) == k.size(0) && (table != nullptr || k.size(0) == k_cache.size(0)) && q.size(1) == k.size(1),
+                  "batch / seq mismatch");
+  STD_TORCH_CHECK(k.size(2) == k_cache.size(1) && q.size(3) == k.size(3), "head count / head_dim mismatch");
+  STD_TORCH_CHECK(q8 || k.size(3) == k_cache.size(3), "head_dim mismatch");
+  STD_TORCH_CHECK(q.stride(-1) == 1 && k.stride(-1) == 1 && k_cache.stride(-1) == 1, "innermost stride must be 1");
+  STD_TORCH_CHECK(start.scalar_type() == ScalarType::Int && start.dim() == 1 && start.numel() == q.size(0) && start.is_contiguous(),
+                  "start must be a contiguous int32 vector with one entry per sequence");
+  MinferRopeParams p{};
+  p.q = q.mutable_data_ptr();
+  p.k = k.const_data_ptr();
+  p.v = v.const_data_ptr();
+  p.k_cache = k_cache.mutable_data_ptr();
+  p.v_cache = v_cache.mutable_data_ptr();
+  p.start = static_cast<const int32_t*>(start.const_data_ptr());
+  for (int i = 0; i < 3; ++i) {
+    p.q_stride[i] = q.stride(i);
+    p.kv_stride[i] = k.stride(i);
+    p.cache_stride[i] = k_cache.stride(i);
+  }
+  p.batch = static_cast<int32_t>(q.size(0));
+  p.seq = static_cast<int32_t>(q.size(1));
+  p.n_heads = static_cast<int32_t>(q.size(2));
+  p.n_kv_heads = static_cast<int32_t>(k.size(2));
+  p.head_dim = static_cast<int32_t>(q.size(3));
+  p.rotary_dim = static_cast<int32_t>(rotary_dim);
+  p.max_len = static_cast<int32_t>(k_cache.size(2));
+  p.freq_base = static_cast<float>(freq_base);
+  if (table != nullptr) {
+    STD_TORCH_CHECK(table->is_cuda() && table->scalar_type() == ScalarType::Int && table->dim() == 2 && table->is_contiguous() &&
+                    table->size(0) == q.size(0), "block_table must be a contiguous CUDA int32 [B, max_pages] tensor");
+    p.block_table = static_cast<const int32_t*>(table->const_data_ptr());
+    p.page_size = static_cast<int32_t>(k_cache.size(2));
+    p.table_stride = static_cast<int32_t>(table->size(1));
+    p.max_len = p.page_size * p.table_stride;
+    p.n_pages = static_cast<int32_t>(k_cache.size(0));
+  }
+  p.status = static_cast<int32_t*>(status_word(q).mutable_data_ptr());
+  p.dtype = dtype_tag(q);
+  p.style = static_cast<int32_t>(style);
+  p.cache_format = q8 ? MINFER_ATTN_KV_Q8_0 : MINFER_ATTN_KV_16BIT;
+  check_rc(minfer_attn_rope_append(&p, current_stream()), "minfer_attn_rope_append");
+}
+
+void rope_kv_append_cuda(int64_t rotary_dim, double freq_base, int64_t style, Tensor& q, const Tensor& k, const Tensor& v,
+                         Tensor& k_cache, Tensor& v_cache, const Tensor& start) {
+  rope_append(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, nullptr, start, false);
+}
+
+void rope_kv_append_q8_cuda(int64_t rotary_dim, double freq_base, int64_t style, Tensor& q, const Tensor& k, const Tensor& v,
+                            Tensor& k_cache, Tensor& v_cache, const Tensor& start) {
+  rope_append(rotary_dim, freq_base, style, q, k, v, k_cache, v_cache, nullptr, start, true);
+}
+
+void rope_kv_append_paged_cuda(int64_t rotary_dim, double freq_base, int64_t style, Tensor& q, const Tensor& k, const Tensor& v,
+                               Tensor& k_pages, Tensor& v_pages, const Tensor& block_table, const Tensor& start) {
+  rope_append(rotary_dim, freq_base, style, q, k, v, k_pages, v_pages, &block_table, start, false);
+}
+
 Tensor attn_status_word_cuda(const Tensor& like) { return status_word(like); }
 
 void attn_set_prefill_cta_limit_cuda(const Tensor& like, int64_t max_ctas) {
@@ -241,6 +369,12 @@ STABLE_TORCH_LIBRARY_IMPL(minfer, CUDA, m) {
   m.impl("flash_attn_causal", TORCH_BOX(&flash_attn_causal_cuda));
   m.impl("flash_attn_decode", TORCH_BOX(&flash_attn_decode_cuda));
   m.impl("flash_attn_decode_paged", TORCH_BOX(&flash_attn_decode_paged_cuda));
+  m.impl("flash_attn_decode_q8", TORCH_BOX(&flash_attn_decode_q8_cuda));
+  m.impl("il_rope", TORCH_BOX(&il_rope_cuda));
+  m.impl("neox_rope", TORCH_BOX(&neox_rope_cuda));
+  m.impl("rope_kv_append", TORCH_BOX(&rope_kv_append_cuda));
+  m.impl("rope_kv_append_q8", TORCH_BOX(&rope_kv_append_q8_cuda));
+  m.impl("rope_kv_append_paged", TORCH_BOX(&rope_kv_append_paged_cuda));
   m.impl("attn_status_word", TORCH_BOX(&attn_status_word_cuda));
   m.impl("attn_set_prefill_cta_limit", TORCH_BOX(&attn_set_prefill_cta_limit_cuda));
 }

@@ -84,14 +84,14 @@ if _binding_choice != "ctypes":
         _C = None
 BINDING = "stable" if _C is not None else "ctypes"
 # ops whose CUDA implementation lives in the extension
-_IN_EXTENSION = ("flash_attn", "flash_attn_causal", "flash_attn_decode", "flash_attn_decode_paged") if _C is not None else ()
+_IN_EXTENSION = tuple(_DEFS) if _C is not None else ()
 
 if _C is None:
     _library = torch.library.Library("minfer", "FRAGMENT")
     for _name, _schema in _DEFS.items():
         _library.define(_name + _schema)
 else:
-    _library = torch.library.Library("minfer", "IMPL")
+    _library = None   # every op has its CUDA implementation in the extension
 
 _status: dict[int, torch.Tensor] = {}
 _workspace: dict[int, torch.Tensor] = {}        # decode split-KV partials, per device

@@ -69,10 +69,10 @@ def test_workspace_size_formula():
     from minfer.kernels.torch_ext import _lib
     L = _lib.lib
     assert L.minfer_attn_decode_default_chunk(64, 8, 8192) == 512
-    assert L.minfer_attn_decode_workspace_bytes(64, 32, 8192, 128, 512) == 64 * 32 * 16 * 130 * 4 + 64 * 32 * 4  # partials + arrival counters
-    assert L.minfer_attn_decode_workspace_bytes(64, 32, 8192, 128, 0) == 64 * 32 * 16 * 130 * 4 + 64 * 32 * 4
+    assert L.minfer_attn_decode_workspace_bytes(64, 32, 8192, 128, 512) == 64 * 32 * 16 * 130 * 4
+    assert L.minfer_attn_decode_workspace_bytes(64, 32, 8192, 128, 0) == 64 * 32 * 16 * 130 * 4
     assert L.minfer_attn_decode_workspace_bytes(64, 32, 8192, 96, 512) == 0
-    assert L.minfer_attn_decode_workspace_bytes(1, 1, 1, 64, 64) == 66 * 4 + 4
+    assert L.minfer_attn_decode_workspace_bytes(1, 1, 1, 64, 64) == 66 * 4
 
 
 def test_prefill_mask_workspace_size():

@@ -87,7 +87,7 @@ def test_chunk_sizes_through_the_c_abi(chunk):
     qd, kd, vd, ld = q.cuda(), kc.cuda(), vc.cuda(), lens.cuda()
     out = torch.zeros(B, H, 1, D, dtype=torch.float16, device="cuda")
     need = _lib.lib.minfer_attn_decode_workspace_bytes(B, H, Lmax, D, chunk)
-    ws = torch.full((need,), 0xFF, dtype=torch.uint8, device="cuda")   # the workspace may hold anything, counters included
+    ws = torch.full((need,), 0xFF, dtype=torch.uint8, device="cuda")   # the workspace may hold anything
     p = _lib.DecodeParams()
     p.q, p.k_cache, p.v_cache, p.lens, p.out = qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), ld.data_ptr(), out.data_ptr()
     p.workspace, p.workspace_bytes = ws.data_ptr(), need
@@ -101,8 +101,7 @@ def test_chunk_sizes_through_the_c_abi(chunk):
     assert rc == 0, _lib.strerror(rc)
     torch.cuda.synchronize()
     check_close(out, want, f"chunk={chunk}")
-    # whichever thread block of a sequence arrives last merges its splits, in split order: repeated calls,
-    # back to back on the same workspace, give the same bits
+    # repeated calls, back to back on the same workspace, give the same bits
     first = out.clone()
     for _ in range(20):
         out.fill_(float("nan"))
