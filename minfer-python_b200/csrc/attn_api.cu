@@ -131,10 +131,11 @@ bool strides_ok(const int64_t* s, int n) {
 }
 
 int32_t default_chunk(int32_t batch, int32_t n_kv_heads, int32_t max_len) {
-  (void)batch;
-  (void)n_kv_heads;
   int32_t c = 512;
   while (c > 64 && c >= 2 * max_len) c >>= 1;
+  // few sequences and heads: shorter chunks, so that the grid still offers every SM two thread blocks (a decode
+  // step of a small batch is a latency problem: each block then walks fewer key tiles in sequence)
+  while (c > 128 && static_cast<int64_t>(batch) * n_kv_heads * ((max_len + c - 1) / c) < 2 * 148) c >>= 1;
   return c;
 }
 

@@ -74,6 +74,11 @@ constexpr int kPolyOf8 = MINFER_ATTN_POLY_OF_8;
 // and [kPSplit, 4).  The PV MMAs of the first piece run under the second piece's exponentials, which
 // shortens the waits for o_done and p_free.  0 publishes P in one piece.
 constexpr int kPSplit = MINFER_ATTN_P_SPLIT;
+#ifndef MINFER_ATTN_BF16_ROUNDED_SUM
+#define MINFER_ATTN_BF16_ROUNDED_SUM 1
+#endif
+// bfloat16 calls: sum the weights after their rounding to bfloat16 (8 significand bits) instead of before it.
+constexpr bool kRoundedSum = MINFER_ATTN_BF16_ROUNDED_SUM != 0;
 static_assert(kPSplit >= 0 && kPSplit <= 3, "P is written as four 32-key chunks");
 constexpr int kPPieces = kPSplit == 0 ? 1 : 2;
 // Tensor-memory plan: S [0,128) used by the two slots in turn, P0 [128,192), P1 [192,256), O0 [256,384),
@@ -254,10 +259,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   constexpr int kNumBars = kKvFull + 2 * kStages;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kIdescS = umma_idesc(kTileM, kTileN, BF16, BF16, false, false);
-  // P is always float16, whatever the type of q/k/v: its values lie in (0, 2^8] (the lazy rescale bounds them), where
-  // float16 resolves 2^-11 against bfloat16's 2^-8 - with a bfloat16 P the rounding of the weights alone reached
-  // the tolerance on rows that average only a few keys.  The PV MMA therefore takes a float16 A and V's type as B.
-  constexpr uint32_t kIdescO = umma_idesc(kTileM, D, false, BF16, false, true);
+  // A and B of one MMA share their 16-bit format: a float16 P beside a bfloat16 V (formats 0 and 1 in the two
+  // fields) is refused by the hardware as an illegal instruction.
+  constexpr uint32_t kIdescO = umma_idesc(kTileM, D, BF16, BF16, false, true);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -821,8 +825,14 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
               p.x = ex2_approx(x.x);
               p.y = ex2_approx(x.y);
             }
-            sum2 = __fadd2_rn(sum2, p);
-            pk[e] = pack2<false>(p.x, p.y);
+            pk[e] = pack2<BF16>(p.x, p.y);
+            if constexpr (BF16 && kRoundedSum) {
+              // the row sum of the weights as the PV MMA will see them (rounded to bfloat16): numerator and
+              // denominator then carry the same rounding, which matters for rows that average only a few keys
+              sum2 = __fadd2_rn(sum2, make_float2(__uint_as_float(pk[e] << 16), __uint_as_float(pk[e] & 0xFFFF0000u)));
+            } else {
+              sum2 = __fadd2_rn(sum2, p);
+            }
           }
           tmem_st16(tmem_p + c * 16, pk);
           if (c == 3 || c + 1 == kPSplit) {

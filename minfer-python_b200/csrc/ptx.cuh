@@ -227,7 +227,7 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_
 //   [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
 //   [15] A major  [16] B major (0 = K-major, 1 = MN-major)
 //   [17,23) N >> 3            [24,29) M >> 4
-// The A and B formats are separate fields: a float16 A may meet a bfloat16 B.
+// The A and B formats are separate fields, but one MMA must use the same 16-bit format for both.
 __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool a_bf16, bool b_bf16, bool a_mn, bool b_mn) {
   return (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | ((b_bf16 ? 1u : 0u) << 10) | ((a_mn ? 1u : 0u) << 15) |
          ((b_mn ? 1u : 0u) << 16) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
