@@ -31,6 +31,8 @@ extern "C" {
 
 #define MINFER_ATTN_ABI_VERSION 5
 
+#define MINFER_ATTN_MAX_PEER_OUT 7   /* output replicas on other GPUs a prefill call can write (8-GPU node) */
+
 /* element types of q/k/v/out */
 #define MINFER_ATTN_F16  0
 #define MINFER_ATTN_BF16 1
@@ -105,6 +107,15 @@ typedef struct MinferAttnPrefillParams {
   int32_t max_ctas;       /* 0: one thread block per SM; n > 0: at most n thread blocks (leaves SMs free for
                              kernels of other streams, e.g. a collective that overlaps this call) */
   int32_t reserved;       /* must be 0 */
+  /* Output replicas on other GPUs (multi-GPU prefill, the all-gather fused into the kernel): every output tile
+   * is stored to `out` AND to each peer_out[i], a device pointer this process can write - the same tensor as
+   * `out` (same shape and strides) in the memory of another GPU, mapped by CUDA IPC or peer access.  The
+   * stores are plain (non-multicast) TMA tensor stores; they are complete when the kernel is, and the caller
+   * orders the readers on the other GPUs after that (a barrier across the ranks).  Causal / unmasked calls
+   * only.  n_peer_out = 0: none. */
+  int32_t n_peer_out;
+  int32_t reserved2;      /* must be 0 */
+  void*   peer_out[MINFER_ATTN_MAX_PEER_OUT];
 } MinferAttnPrefillParams;
 
 int minfer_attn_prefill(const MinferAttnPrefillParams* params, void* stream);

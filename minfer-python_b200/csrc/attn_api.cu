@@ -184,8 +184,13 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
     return MINFER_ATTN_EINVAL;
   if (!(p->softmax_scale >= 0.f)) return MINFER_ATTN_EINVAL;
   if (p->batch > 65535 || p->n_heads > 65535) return MINFER_ATTN_EUNSUPPORTED;
-  if (p->flags != 0 || p->reserved != 0) return MINFER_ATTN_EUNSUPPORTED;
+  if (p->flags != 0 || p->reserved != 0 || p->reserved2 != 0) return MINFER_ATTN_EUNSUPPORTED;
   if (p->max_ctas < 0) return MINFER_ATTN_EINVAL;
+  if (p->n_peer_out < 0 || p->n_peer_out > MINFER_ATTN_MAX_PEER_OUT) return MINFER_ATTN_EINVAL;
+  for (int i = 0; i < p->n_peer_out; ++i)
+    if (p->peer_out[i] == nullptr || !aligned16(p->peer_out[i])) return MINFER_ATTN_EINVAL;
+  // the fused output exchange exists for the causal / unmasked form (a dense-mask call may write rows directly)
+  if (p->n_peer_out > 0 && !p->causal && p->mask != nullptr) return MINFER_ATTN_EUNSUPPORTED;
   // the masked kernel's tile list holds 1024 key tiles
   if (!p->causal && p->mask != nullptr && p->seq_k > 128 * 1024) return MINFER_ATTN_EUNSUPPORTED;
   int rc = check_device();
@@ -206,6 +211,17 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
   alignas(64) CUtensorMap to;
   rc = make_tensor_map(&to, p->out, bf16, p->head_dim, p->batch, p->n_heads, p->seq_q, p->out_stride, a.out_pos, 32);
   if (rc != MINFER_ATTN_OK) return rc;
+
+  static_assert(MINFER_ATTN_MAX_PEER_OUT == kMaxPeerOut, "peer output count");
+  alignas(64) PeerMaps peers;
+  for (int i = 0; i < kMaxPeerOut; ++i) {
+    // unused entries repeat the local map, so that the kernel's parameter block never holds garbage
+    int32_t pos_unused[3];
+    void* base = i < p->n_peer_out ? p->peer_out[i] : p->out;
+    rc = make_tensor_map(&peers.m[i], base, bf16, p->head_dim, p->batch, p->n_heads, p->seq_q, p->out_stride, pos_unused, 32);
+    if (rc != MINFER_ATTN_OK) return rc;
+  }
+  a.n_peers = p->n_peer_out;
 
   a.out = p->out;
   a.mask = p->causal ? nullptr : p->mask;
@@ -239,7 +255,7 @@ int minfer_attn_prefill(const MinferAttnPrefillParams* p, void* stream) {
 
   a.pair_heads = (a.group % 2 == 0) ? 1 : 0;
   a.max_ctas = p->max_ctas;
-  return cuda_result(launch_prefill_persist(tq, tk, tv, to, a, p->head_dim, bf16, static_cast<cudaStream_t>(stream)));
+  return cuda_result(launch_prefill_persist(tq, tk, tv, to, peers, a, p->head_dim, bf16, static_cast<cudaStream_t>(stream)));
 }
 
 size_t minfer_attn_prefill_workspace_bytes(int32_t batch, int32_t seq_q, int32_t seq_k) {

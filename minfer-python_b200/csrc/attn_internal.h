@@ -31,6 +31,7 @@ struct PrefillArgs {
   int32_t mask_vec;       // mask rows may be read with 16-byte loads
   int32_t pair_heads;     // slots are two heads of one kv head (else two row tiles of one head)
   int32_t max_ctas;       // upper bound on the grid (0: one CTA per SM)
+  int32_t n_peers;        // output replicas on other GPUs: every output tile is also stored through PeerMaps::m[0 .. n_peers)
   int32_t items_x, items_y;  // persistent kernel: work-item grid (query tile [pairs], head [pairs]); set by its launcher
   int32_t order_by_kv_set;   // persistent kernel, dynamic claiming: item order (see its launcher)
   float scale_log2;       // softmax scale * log2(e)
@@ -41,8 +42,15 @@ struct PrefillArgs {
   int32_t out_pos[3];  // coordinate slots of the output tensor map (persistent kernel only)
 };
 
+// Output tensor maps of the replicas of `out` on other GPUs (PrefillArgs::n_peers of them are valid).
+constexpr int kMaxPeerOut = 7;
+struct PeerMaps {
+  CUtensorMap m[kMaxPeerOut];
+};
+
 cudaError_t launch_prefill_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                                   const CUtensorMap& to, const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream);
+                                   const CUtensorMap& to, const PeerMaps& peers, const PrefillArgs& a, int head_dim,
+                                   bool bf16, cudaStream_t stream);
 
 // Classifies every 128 x 128 tile of a dense [batch, 1, seq_q, seq_k] byte mask: 0 = no byte set,
 // 1 = every in-range byte set, 2 = mixed.  cls is [batch, ceil(seq_q/128), ceil(seq_k/128)].

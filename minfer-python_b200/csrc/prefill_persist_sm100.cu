@@ -243,7 +243,7 @@ template <int D, bool BF16, bool kMasked>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-                       const PrefillArgs a) {
+                       const __grid_constant__ PeerMaps tm_peers, const PrefillArgs a) {
   constexpr int kDB = D / 64;
   constexpr int kTileBytes = kDB * kBlockBytes;
 #ifndef MINFER_ATTN_STAGES128
@@ -898,6 +898,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           __syncwarp();
           if (lane == 0 && row0 < a.seq_q) {
             tma_store_4d(&tm_o, stage, h * 64, c1, c2, c3);
+            // multi-GPU prefill: the same box goes to the replicas of `out` on the other GPUs (plain tensor
+            // stores over NVLink, no multicast), so the output exchange rides along tile by tile
+            for (int pr = 0; pr < a.n_peers; ++pr) tma_store_4d(&tm_peers.m[pr], stage, h * 64, c1, c2, c3);
             bulk_commit();
           }
         }
@@ -925,7 +928,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
 template <int D, bool BF16, bool kMasked>
 cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                               const CUtensorMap& to, PrefillArgs a,
+                               const CUtensorMap& to, const PeerMaps& peers, PrefillArgs a,
                                cudaStream_t stream) {
   constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
   // tiles, epilogue staging, barriers and ring heads, (dense masks) the ring's bit planes, alignment slack:
@@ -964,7 +967,7 @@ cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, con
     e = cudaMemsetAsync(a.counter, 0, sizeof(int), stream);
     if (e != cudaSuccess) return e;
   }
-  prefill_persist_kernel<D, BF16, kMasked><<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, a);
+  prefill_persist_kernel<D, BF16, kMasked><<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, peers, a);
   return cudaGetLastError();
 }
 
@@ -979,19 +982,20 @@ extern "C" int minfer_attn_debug_read_trace(void* dst, size_t bytes) {
 #endif
 
 cudaError_t launch_prefill_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                                   const CUtensorMap& to, const PrefillArgs& a, int head_dim, bool bf16, cudaStream_t stream) {
+                                   const CUtensorMap& to, const PeerMaps& peers, const PrefillArgs& a, int head_dim,
+                                   bool bf16, cudaStream_t stream) {
   if (a.mask != nullptr) {
     if (head_dim == 128)
-      return bf16 ? launch_persist_one<128, true, true>(tq, tk, tv, to, a, stream)
-                  : launch_persist_one<128, false, true>(tq, tk, tv, to, a, stream);
-    return bf16 ? launch_persist_one<64, true, true>(tq, tk, tv, to, a, stream)
-                : launch_persist_one<64, false, true>(tq, tk, tv, to, a, stream);
+      return bf16 ? launch_persist_one<128, true, true>(tq, tk, tv, to, peers, a, stream)
+                  : launch_persist_one<128, false, true>(tq, tk, tv, to, peers, a, stream);
+    return bf16 ? launch_persist_one<64, true, true>(tq, tk, tv, to, peers, a, stream)
+                : launch_persist_one<64, false, true>(tq, tk, tv, to, peers, a, stream);
   }
   if (head_dim == 128)
-    return bf16 ? launch_persist_one<128, true, false>(tq, tk, tv, to, a, stream)
-                : launch_persist_one<128, false, false>(tq, tk, tv, to, a, stream);
-  return bf16 ? launch_persist_one<64, true, false>(tq, tk, tv, to, a, stream)
-              : launch_persist_one<64, false, false>(tq, tk, tv, to, a, stream);
+    return bf16 ? launch_persist_one<128, true, false>(tq, tk, tv, to, peers, a, stream)
+                : launch_persist_one<128, false, false>(tq, tk, tv, to, peers, a, stream);
+  return bf16 ? launch_persist_one<64, true, false>(tq, tk, tv, to, peers, a, stream)
+              : launch_persist_one<64, false, false>(tq, tk, tv, to, peers, a, stream);
 }
 
 }  // namespace minfer_attn

@@ -14,7 +14,8 @@ backend, where the tests drive it with a stand-in attention function.
 Prefill output exchange.  Every rank ends with the full [B, H, L, D] output, and every byte is
 written exactly once, straight into its final place: a rank's attention call writes its heads
 into a strided view of the full tensor, and the exchange delivers each peer's heads into theirs.
-The exchange is cut into head blocks: a block of a rank's heads is, per batch element, one
+(A second form, prefill_head_parallel_fused, needs no exchange step at all: the attention kernel itself stores
+every output tile into the other ranks' output tensors.)  The exchange is cut into head blocks: a block of a rank's heads is, per batch element, one
 contiguous [heads, L, D] region of the output, so a block travels as plain point-to-point
 transfers (grouped into one NCCL launch) with no staging copy on either side.  The attention of
 block i+1 runs while block i travels; the two compute streams alternate, so the thread blocks
@@ -106,6 +107,66 @@ def _exchange_block(out: torch.Tensor, hp: int, qsl: slice, world: int, rank: in
             ops.append(dist.P2POp(dist.irecv, out[b, p * hp + qsl.start: p * hp + qsl.stop], peer, group))
     for w in dist.batch_isend_irecv(ops):
         w.wait()
+
+
+class PeerOutputs:
+    """A [B, H, L, D] output tensor per rank that every other rank of the node can write: the buffers are shared
+    through CUDA IPC (one process per GPU), so a kernel on rank r can store its heads straight into the memory of
+    all the others.  `local` is this rank's tensor; `peer_ptr(view)` gives, for a view of `local`, the addresses
+    of the same view inside every other rank's tensor, in rank order."""
+
+    def __init__(self, shape, dtype, device, group=None):
+        from torch.multiprocessing.reductions import reduce_tensor
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.local = torch.zeros(shape, dtype=dtype, device=device)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, reduce_tensor(self.local), group=group)
+        self._peers = []          # keeps the mappings alive
+        self._bases = []
+        my_index = self.local.device.index
+        for r, (rebuild, args) in enumerate(handles):
+            if r == self.rank:
+                continue
+            # Open the peer's IPC handle with THIS rank's device current (argument 6 of torch's rebuild function is
+            # the device the storage is opened on): the mapping then belongs to this device's context, peer access
+            # to the owner is enabled by the open itself, and no context is created on any other GPU.
+            args = list(args)
+            args[6] = my_index
+            t = rebuild(*args)
+            self._peers.append(t)
+            self._bases.append(t.data_ptr())
+        dist.barrier(group=group)
+
+    def peer_ptrs(self, view: torch.Tensor):
+        off = view.data_ptr() - self.local.data_ptr()
+        assert 0 <= off < self.local.numel() * self.local.element_size(), "not a view of the shared output"
+        return [b + off for b in self._bases]
+
+
+def prefill_head_parallel_fused(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, outputs: PeerOutputs,
+                                inputs_are_shards: bool = False) -> torch.Tensor:
+    """Head-parallel causal prefill with the output exchange inside the attention kernel: this rank's kv-head
+    group is computed once and every output tile is stored into the local output and, over NVLink, into the
+    output tensors of all other ranks (`outputs`, shared through CUDA IPC), so the transfer overlaps the math tile
+    by tile and no SM is set aside for a collective.  A barrier across the ranks (the one NCCL call) ends the step:
+    after it every rank holds the full [B, H, L, D] result in outputs.local.  CUDA only."""
+    from .kernels.torch_ext.ops import flash_attn_causal_multi_out
+    group = outputs.group
+    world, rank = outputs.world, outputs.rank
+    out = outputs.local
+    B, H, L, D = out.shape
+    Hkv = k.shape[1] * world if inputs_are_shards else k.shape[1]
+    qs, kvs = head_shard(H, Hkv, world, rank)
+    q_loc = q if inputs_are_shards else q[:, qs]
+    k_loc = k if inputs_are_shards else k[:, kvs]
+    v_loc = v if inputs_are_shards else v[:, kvs]
+    mine = out[:, qs]
+    flash_attn_causal_multi_out(q_loc, k_loc, v_loc, mine, outputs.peer_ptrs(mine))
+    if world > 1:
+        dist.barrier(group=group)
+    return out
 
 
 def prefill_head_parallel(attn_fn: Callable, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,

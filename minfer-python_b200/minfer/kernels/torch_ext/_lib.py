@@ -57,6 +57,9 @@ class PrefillParams(ctypes.Structure):
         ("workspace_bytes", ctypes.c_size_t),
         ("max_ctas", ctypes.c_int32),
         ("reserved", ctypes.c_int32),
+        ("n_peer_out", ctypes.c_int32),
+        ("reserved2", ctypes.c_int32),
+        ("peer_out", ctypes.c_void_p * 7),
     ]
 
 

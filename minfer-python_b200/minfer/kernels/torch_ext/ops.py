@@ -148,8 +148,11 @@ def _check_qkv(q, k, v, out):
     torch._check(q.size(1) % k.size(1) == 0, lambda: "n_heads must be a multiple of n_kv_heads")
 
 
-def _prefill(q, k, v, mask, out, causal: bool) -> None:
+def _prefill(q, k, v, mask, out, causal: bool, peer_out=()) -> None:
     p = _lib.PrefillParams()
+    p.n_peer_out = len(peer_out)
+    for i, ptr in enumerate(peer_out):
+        p.peer_out[i] = ptr
     p.q, p.k, p.v, p.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
     p.mask = mask.data_ptr() if mask is not None else None
     p.status = _status_word(q.device).data_ptr()
@@ -189,6 +192,18 @@ def _flash_attn_causal_cuda(q, k, v, out) -> None:
     _check_qkv(q, k, v, out)
     torch._check(k.size(2) >= q.size(2), lambda: "causal attention requires seq_k >= seq_q")
     _prefill(q, k, v, None, out, causal=True)
+
+
+def flash_attn_causal_multi_out(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, peer_out) -> None:
+    """flash_attn_causal whose kernel stores every output tile to `out` and to each address in `peer_out`: device
+    pointers (ints), writable from this process, of the same [B, H, L, D] view in the memory of up to seven other
+    GPUs.  The multi-GPU harness uses it to fuse the output exchange of head-parallel prefill into the attention
+    kernel (minfer.dist.PeerOutputs builds the pointers).  The stores are complete when the kernel is; ordering the
+    readers on the other GPUs after that is the caller's business.  Always goes through the ctypes binding."""
+    _check_qkv(q, k, v, out)
+    torch._check(k.size(2) >= q.size(2), lambda: "causal attention requires seq_k >= seq_q")
+    torch._check(len(peer_out) <= 7, lambda: "at most 7 output replicas")
+    _prefill(q, k, v, None, out, causal=True, peer_out=tuple(int(x) for x in peer_out))
 
 
 def _workspace_for(device: torch.device, nbytes: int, cache: dict, stream: int = 0) -> torch.Tensor:

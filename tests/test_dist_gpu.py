@@ -58,6 +58,20 @@ def _worker(rank, world, port, result_dir):
         torch.cuda.synchronize()
         assert torch.equal(buf, single[:1]), "B=1 in-place all-gather"
 
+        # the exchange fused into the kernel: every rank's output tensor is shared through CUDA IPC and the
+        # attention kernel stores its tiles into all of them; twice in a row on the same buffers
+        from minfer.dist import PeerOutputs, prefill_head_parallel_fused
+        for Bf in (1, 2):
+            outs = PeerOutputs((Bf, H, L, D), torch.float16, torch.device("cuda", rank))
+            for _ in range(2):
+                outs.local.fill_(float("nan"))
+                torch.cuda.synchronize()
+                dist.barrier()
+                res = prefill_head_parallel_fused(q[:Bf], k[:Bf], v[:Bf], outs)
+                torch.cuda.synchronize()
+                assert torch.equal(res, single[:Bf]), f"fused head-parallel prefill differs (B={Bf})"
+            del outs
+
         Bd, Lmax = 8, 1500
         qd = torch.randn(Bd, H, 1, D, generator=g).half().cuda()
         kc = torch.randn(Bd, Hkv, Lmax, D, generator=g).half().cuda()
