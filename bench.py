@@ -498,8 +498,8 @@ def config4_record(kerns, args, rank, world, dev, peaks):
     # (shared through CUDA IPC) as it is produced; one barrier across the ranks ends the step
     ms_fused, fused_ok, fused_err = None, None, None
     try:
-        if os.environ.get("MINFER_BENCH_FUSED", "0") in ("", "0"):
-            raise RuntimeError("fused form not requested (MINFER_BENCH_FUSED=1 enables it)")
+        if os.environ.get("MINFER_BENCH_FUSED", "1") in ("", "0"):
+            raise RuntimeError("fused form switched off (MINFER_BENCH_FUSED=0)")
         shared = PeerOutputs((B, H, L, D), torch.bfloat16, dev)
         ms_fused = time_gpu(lambda: prefill_head_parallel_fused(q_s, k_s, v_s, shared, inputs_are_shards=True), n, 2, world, dev)
         check_status(dev)
@@ -510,6 +510,7 @@ def config4_record(kerns, args, rank, world, dev, peaks):
         dist.all_reduce(flo, op=dist.ReduceOp.MIN)
         fused_ok = bool(torch.equal(fhi, flo)) and bool(torch.equal(shared.local[:, qs], reference)) and bool(torch.isfinite(fsums).all())
         fused_ok = reduce_ranks(0.0 if fused_ok else 1.0, world, dev) == 0.0
+        shared.close()
         del shared
     except Exception as e:  # noqa: BLE001  (peer mapping unavailable: the NCCL forms stand)
         fused_err = repr(e)[:200]

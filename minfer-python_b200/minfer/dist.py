@@ -139,6 +139,13 @@ class PeerOutputs:
             self._bases.append(t.data_ptr())
         dist.barrier(group=group)
 
+    def close(self) -> None:
+        """Drop this rank's mappings of the other ranks' tensors (every rank, before any of them frees its own)."""
+        self._peers.clear()
+        self._bases.clear()
+        torch.cuda.synchronize(self.local.device)
+        dist.barrier(group=self.group)
+
     def peer_ptrs(self, view: torch.Tensor):
         off = view.data_ptr() - self.local.data_ptr()
         assert 0 <= off < self.local.numel() * self.local.element_size(), "not a view of the shared output"

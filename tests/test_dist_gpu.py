@@ -70,6 +70,7 @@ def _worker(rank, world, port, result_dir):
                 res = prefill_head_parallel_fused(q[:Bf], k[:Bf], v[:Bf], outs)
                 torch.cuda.synchronize()
                 assert torch.equal(res, single[:Bf]), f"fused head-parallel prefill differs (B={Bf})"
+            outs.close()
             del outs
 
         Bd, Lmax = 8, 1500
