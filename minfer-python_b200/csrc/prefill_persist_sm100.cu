@@ -722,6 +722,15 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         const int kv0 = i * kTileN;
         const int j = kMasked ? jm : i;
+        // dense masks: the mask bytes of a mixed tile (this thread's row, 128 keys: one or two cache lines) are
+        // prefetched before the wait for the scores, so that their trip from L2 or HBM runs under that wait and
+        // the tensor-memory load instead of after them (holding them in registers across the wait spills)
+        if constexpr (kMasked) {
+          if (mixed) {
+            prefetch_l1(mrow + kv0);
+            prefetch_l1(mrow + min(kv0 + kTileN, a.seq_k) - 1);
+          }
+        }
         P_ACC(acc_c = clock64());
         P_TL(s, j, 0);
         if (!(ok = mbar_wait(&bars[kSFull + s], jt & 1u, abort_flag))) { report_p(a.status, 40); break; }
