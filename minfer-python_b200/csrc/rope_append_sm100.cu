@@ -298,12 +298,14 @@ cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, bool neox, cudaStre
   const int chunks = a.head_dim / 8;
   const int work_chunks = neox ? chunks - a.rotary_dim / 16 : chunks;
   const long long threads = static_cast<long long>(a.batch) * a.seq * work_chunks;
-  // Slices over the token's rows (query heads + k heads + v heads): enough of them that about 128 k threads are
-  // in flight, but no fewer than four rows per thread where there is that much work (every thread computes the
-  // sines and cosines of its chunk's angles once, whatever its number of rows)
+  // Slices over the token's rows (query heads + k heads + v heads): enough of them that the grid is about eight
+  // waves of the three 256-thread blocks an SM holds (with one slice a prefill-sized call is 2.3 waves and a
+  // quarter of the GPU idles through the last one), but no fewer than four rows per thread where there is that much
+  // work (every thread computes the sines and cosines of its chunk's angles once, whatever its number of rows)
   const int n_rows = (a.q != nullptr ? a.n_heads : 0) + (a.k != nullptr ? a.n_kv_heads : 0) +
                      (a.v != nullptr && a.v_cache != nullptr ? a.n_kv_heads : 0);
-  long long slices = (131072 + threads - 1) / threads;
+  const long long blocks_x = (threads + 255) / 256;
+  long long slices = (8 * 3 * 148 + blocks_x - 1) / blocks_x;
   const long long max_slices = threads >= 65536 ? (n_rows + 3) / 4 : n_rows;
   if (slices > max_slices) slices = max_slices;
   if (slices < 1) slices = 1;

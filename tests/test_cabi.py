@@ -51,6 +51,16 @@ def test_invalid_arguments_are_rejected_without_a_device():
     p.q_stride[2] = 128
     p.causal, p.seq_k = 1, 64
     assert L.minfer_attn_prefill(ctypes.byref(p), None) == 1          # causal with fewer keys than queries
+    p.causal, p.seq_k = 1, 128
+    p.n_peer_out = 8
+    assert L.minfer_attn_prefill(ctypes.byref(p), None) == 1          # more output replicas than the struct holds
+    p.n_peer_out = 1
+    assert L.minfer_attn_prefill(ctypes.byref(p), None) == 1          # a null replica pointer
+    p.peer_out[0] = 0x2000
+    p.causal, p.mask = 0, 0x3000
+    assert L.minfer_attn_prefill(ctypes.byref(p), None) == 2          # replicas with a dense mask: unsupported
+    p.n_peer_out, p.mask, p.flags = 0, None, 4
+    assert L.minfer_attn_prefill(ctypes.byref(p), None) == 2          # reserved flags word
     d = _lib.DecodeParams()
     assert L.minfer_attn_decode(ctypes.byref(d), None) == 1
     d.q = d.k_cache = d.v_cache = d.lens = d.out = 0x1000
