@@ -397,6 +397,8 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
   }
 }
 
+// The merge is a latency problem (a few hundred bytes per thread, every load a trip to L2 or HBM), so the loads are
+// issued eight at a time: the (max, sum) pairs of eight splits, then the eight partial outputs they weight.
 template <int D, bool BF16>
 __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
   const int h = blockIdx.x;
@@ -405,13 +407,33 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
   const int len = min(a.lens[b], a.max_len);
   const int ns = (len + a.chunk - 1) / a.chunk;
   const size_t p0 = (static_cast<size_t>(b) * a.n_heads + h) * a.n_split;
+  const float2* ml = reinterpret_cast<const float2*>(a.part_ml) + p0;
+  const float* po = a.part_o + p0 * D + d;
+  constexpr int kBatch = 8;
   float M = -INFINITY;
-  for (int s = 0; s < ns; ++s) M = fmaxf(M, a.part_ml[(p0 + s) * 2]);
+  for (int s0 = 0; s0 < ns; s0 += kBatch) {
+    float m[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) m[j] = (s0 + j < ns) ? ml[s0 + j].x : -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) M = fmaxf(M, m[j]);
+  }
   float o = 0.f, l = 0.f;
-  for (int s = 0; s < ns; ++s) {
-    const float sc = ex2_approx(a.part_ml[(p0 + s) * 2] - M);
-    l += sc * a.part_ml[(p0 + s) * 2 + 1];
-    o += sc * a.part_o[(p0 + s) * D + d];
+  for (int s0 = 0; s0 < ns; s0 += kBatch) {
+    float2 w[kBatch];
+    float x[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const bool live = s0 + j < ns;
+      w[j] = live ? ml[s0 + j] : make_float2(-INFINITY, 0.f);
+      x[j] = live ? po[static_cast<size_t>(s0 + j) * D] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const float sc = (w[j].x == -INFINITY) ? 0.f : ex2_approx(w[j].x - M);
+      l += sc * w[j].y;
+      o += sc * x[j];
+    }
   }
   const float r = (l > 0.f) ? o / l : 0.f;
   uint8_t* op = reinterpret_cast<uint8_t*>(a.out) +

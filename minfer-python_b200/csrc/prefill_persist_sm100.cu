@@ -74,6 +74,9 @@ constexpr int kPolyOf8 = MINFER_ATTN_POLY_OF_8;
 // and [kPSplit, 4).  The PV MMAs of the first piece run under the second piece's exponentials, which
 // shortens the waits for o_done and p_free.  0 publishes P in one piece.
 constexpr int kPSplit = MINFER_ATTN_P_SPLIT;
+#ifndef MINFER_ATTN_MASK_PREFETCH
+#define MINFER_ATTN_MASK_PREFETCH 1
+#endif
 #ifndef MINFER_ATTN_BF16_ROUNDED_SUM
 #define MINFER_ATTN_BF16_ROUNDED_SUM 0
 #endif
@@ -725,7 +728,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // dense masks: the mask bytes of a mixed tile (this thread's row, 128 keys: one or two cache lines) are
         // prefetched before the wait for the scores, so that their trip from L2 or HBM runs under that wait and
         // the tensor-memory load instead of after them (holding them in registers across the wait spills)
-        if constexpr (kMasked) {
+        if constexpr (kMasked && MINFER_ATTN_MASK_PREFETCH) {
           if (mixed) {
             prefetch_l1(mrow + kv0);
             prefetch_l1(mrow + min(kv0 + kTileN, a.seq_k) - 1);
