@@ -96,11 +96,11 @@ def _worker(rank, world, port, result_dir):
         want1 = O.attention_f64(q, k1, v1, causal=True)
         assert torch.equal(prefill_head_parallel(prefill_fn, q, k1, v1, blocks=2), want1), "query-head blocks"
 
-        Bd, Lmax = 6, 40
+        Bd, Lmax = 8, 40
         qd = torch.randn(Bd, H, 1, D, generator=g)
         kc = torch.randn(Bd, Hkv, Lmax, D, generator=g)
         vc = torch.randn(Bd, Hkv, Lmax, D, generator=g)
-        lens = torch.tensor([40, 3, 17, 25, 1, 33], dtype=torch.int32)
+        lens = torch.tensor([40, 3, 17, 25, 1, 33, 40, 9], dtype=torch.int32)
         shards = DecodeShards(lens.tolist(), world)
         mine = torch.tensor(shards.mine(rank))
         outd = decode_batch_parallel(decode_fn, qd[mine], kc[mine], vc[mine], lens[mine], shards)
@@ -110,7 +110,9 @@ def _worker(rank, world, port, result_dir):
         dist.destroy_process_group()
 
 
-def test_two_rank_gloo_harness(tmp_path):
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_gloo_harness(tmp_path, world):
+    """Two ranks (two kv heads each) and four ranks (one kv head each: the exchange then has three peers and the
+    head blocks are cut inside the one kv head's query heads)."""
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+    assert sorted(os.listdir(tmp_path)) == [f"ok{r}" for r in range(world)]
