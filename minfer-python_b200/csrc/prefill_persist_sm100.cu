@@ -57,8 +57,12 @@ constexpr int kBlockBytes = 128 * 128;
 constexpr int kEpiBytes = 32 * 128;  // 32 rows x 64 columns of 16-bit output per softmax warp
 constexpr int kThreads = 384;  // softmax 0 (warps 0-3), softmax 1 (4-7), score MMAs (8), scheduler + TMA (9), PV MMAs (10), idle (11)
 // setmaxnreg split of the 384 x 168 launch allocation: 8 x 208 + 4 x 88 = 12 x 168
-constexpr int kRegsSoftmax = 208;
-constexpr int kRegsOther = 88;
+#ifndef MINFER_ATTN_REGS_SOFTMAX
+#define MINFER_ATTN_REGS_SOFTMAX 208
+#define MINFER_ATTN_REGS_OTHER 88
+#endif
+constexpr int kRegsSoftmax = MINFER_ATTN_REGS_SOFTMAX;
+constexpr int kRegsOther = MINFER_ATTN_REGS_OTHER;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 #ifndef MINFER_ATTN_POLY_OF_8
 #define MINFER_ATTN_POLY_OF_8 0
@@ -74,6 +78,11 @@ constexpr int kPolyOf8 = MINFER_ATTN_POLY_OF_8;
 // and [kPSplit, 4).  The PV MMAs of the first piece run under the second piece's exponentials, which
 // shortens the waits for o_done and p_free.  0 publishes P in one piece.
 constexpr int kPSplit = MINFER_ATTN_P_SPLIT;
+#ifndef MINFER_ATTN_DEFER_P_ARRIVE
+#define MINFER_ATTN_DEFER_P_ARRIVE 0
+#endif
+// Publish the first piece of P after the NEXT chunk's exponentials instead of right after its own stores.
+constexpr bool kDeferPArrive = MINFER_ATTN_DEFER_P_ARRIVE != 0;
 #ifndef MINFER_ATTN_MASK_PREFETCH
 #define MINFER_ATTN_MASK_PREFETCH 1
 #endif
@@ -849,8 +858,18 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
               sum2 = __fadd2_rn(sum2, p);
             }
           }
+          if constexpr (kDeferPArrive) {
+            // the first piece is published one chunk late: its tensor-memory stores have long landed by the time
+            // the next chunk's exponentials are done, so the wait for them costs nothing
+            if (kPPieces == 2 && c == kPSplit) {
+              tc_wait_st();
+              tc_fence_before();
+              mbar_arrive(&bars[kPFull + 4 * s]);
+              P_TL(s, j, 4);
+            }
+          }
           tmem_st16(tmem_p + c * 16, pk);
-          if (c == 3 || c + 1 == kPSplit) {
+          if (c == 3 || (!kDeferPArrive && c + 1 == kPSplit)) {
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(&bars[kPFull + 4 * s + (c == 3 ? kPPieces - 1 : 0)]);
