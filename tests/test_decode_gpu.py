@@ -143,3 +143,35 @@ def test_argument_errors_raise(kerns):
         kerns.flash_attn_decode(q, kc, kc, lens[:1], out)
     with pytest.raises(RuntimeError):
         kerns.flash_attn_decode(q.expand(2, 8, 2, 128), kc, kc, lens, out.expand(2, 8, 2, 128))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_shapes_against_the_oracle(kerns, seed):
+    """Seeded random batch, heads, GQA group up to 16, head_dim, type, padded length and lengths (empty sequences
+    included), contiguous or [B, Lmax, Hkv, D]-stored caches."""
+    g = torch.Generator().manual_seed(7000 + seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))  # noqa: E731
+    B, Hkv, group = r(1, 9), r(1, 4), [1, 2, 3, 4, 5, 8, 16][r(0, 6)]
+    H, D = Hkv * group, [64, 128][r(0, 1)]
+    dtype = [torch.float16, torch.bfloat16][r(0, 1)]
+    Lmax = r(1, 3000)
+    lens = torch.randint(0, Lmax + 1, (B,), generator=g, dtype=torch.int32)
+    lens[r(0, B - 1)] = Lmax
+    q = torch.randn(B, H, 1, D, generator=g).to(dtype)
+    if r(0, 1):
+        kc = torch.randn(B, Lmax, Hkv, D, generator=g).to(dtype).transpose(1, 2)
+        vc = torch.randn(B, Lmax, Hkv, D, generator=g).to(dtype).transpose(1, 2)
+    else:
+        kc = torch.randn(B, Hkv, Lmax, D, generator=g).to(dtype)
+        vc = torch.randn(B, Hkv, Lmax, D, generator=g).to(dtype)
+    want = O.attention_f64(q, kc, vc, lens=lens)
+    got = run_decode(kerns, q, kc, vc, lens)
+    assert torch.count_nonzero(got[lens == 0]) == 0
+    live = lens > 0
+    what = f"seed {seed}: B={B} H={H} Hkv={Hkv} D={D} Lmax={Lmax} {dtype}"
+    if dtype == torch.bfloat16:
+        from _util import bf16_tolerance_counts
+        counts = bf16_tolerance_counts(got[live], want[live])
+        assert counts["fail_with_half_ulp"] <= max(2, 2e-5 * counts["elements"]), what + f" {counts}"
+    else:
+        check_close(got[live], want[live], what)

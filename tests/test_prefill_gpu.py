@@ -456,3 +456,42 @@ def test_opcheck(kerns):
                           test_utils=("test_schema", "test_faketensor"))
     torch.library.opcheck(torch.ops.minfer.flash_attn_causal.default, (q, k, v, out),
                           test_utils=("test_schema", "test_faketensor"))
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_shapes_against_the_oracle(kerns, seed):
+    """Seeded random draws of everything a caller may vary - batch, heads, GQA group (powers of two or not),
+    sequence lengths (ragged against the 128-row tiles, more keys than queries), head_dim, type, layout
+    (contiguous or the reference callers' transposed views), causal entry or a random dense mask."""
+    g = torch.Generator().manual_seed(9000 + seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))  # noqa: E731
+    B, Hkv, group = r(1, 3), r(1, 3), [1, 2, 3, 4, 6, 8][r(0, 5)]
+    H, D = Hkv * group, [64, 128][r(0, 1)]
+    dtype = [torch.float16, torch.bfloat16][r(0, 1)]
+    Lq = r(1, 700)
+    causal = r(0, 1) == 1
+    Lk = Lq + (r(0, 300) if causal and r(0, 1) else 0)
+    transposed = r(0, 1) == 1
+    if transposed:
+        q = torch.randn(B, Lq, H * D, generator=g).to(dtype).view(B, Lq, H, D).transpose(1, 2)
+        k = torch.randn(B, Lk, Hkv * D, generator=g).to(dtype).view(B, Lk, Hkv, D).transpose(1, 2)
+        v = torch.randn(B, Lk, Hkv * D, generator=g).to(dtype).view(B, Lk, Hkv, D).transpose(1, 2)
+    else:
+        q = torch.randn(B, H, Lq, D, generator=g).to(dtype)
+        k = torch.randn(B, Hkv, Lk, D, generator=g).to(dtype)
+        v = torch.randn(B, Hkv, Lk, D, generator=g).to(dtype)
+    what = f"seed {seed}: B={B} H={H} Hkv={Hkv} D={D} Lq={Lq} Lk={Lk} {dtype} causal={causal} transposed={transposed}"
+    if causal:
+        want = O.attention_f64(q, k, v, causal=True)
+        got = run_causal(kerns, q, k, v)
+    else:
+        mask = torch.rand(B, 1, Lq, Lk, generator=g) < [0.05, 0.5, 0.95][r(0, 2)]
+        mask[:, :, :, 0] |= torch.rand(B, 1, Lq, generator=g) < 0.9      # most rows see at least one key, some none
+        want = O.attention_f64(q, k, v, mask=mask)
+        got = run_masked(kerns, q, k, v, mask)
+    if dtype == torch.bfloat16:
+        # short rows of a bfloat16 call: see check_close_bf16_rows; a dense random mask makes any row short
+        counts = bf16_tolerance_counts(got, want)
+        assert counts["fail_with_half_ulp"] <= max(2, 2e-5 * counts["elements"]), what + f" {counts}"
+    else:
+        check_close(got, want, what)
