@@ -40,12 +40,7 @@ namespace minfer_attn {
 namespace {
 
 constexpr int kWarps = 4;
-#ifndef MINFER_DECODE_Q8_CTAS
-#define MINFER_DECODE_Q8_CTAS 3
-#define MINFER_DECODE_Q8_STAGES 3
-#endif
-// cp.async ring depth per warp: 3 for the 16-bit caches; the Q8_0 form takes its own (tuning macro)
-template <bool Q8> constexpr int stages_of() { return Q8 ? MINFER_DECODE_Q8_STAGES : 3; }
+constexpr int kStages = 3;
 constexpr int kTileKeys = 16;
 
 // kept out of line: the error path must not cost the streaming loop registers
@@ -115,8 +110,9 @@ __device__ __forceinline__ void dequant8(const uint8_t* block, int part, bool li
 // Paged: the caches are pools of pages reached through a.block_table (a separate instantiation, so that the
 // contiguous form keeps its registers).
 template <int D, bool BF16, bool Q8, bool Paged>
-__global__ void __launch_bounds__(kWarps * 32, Q8 ? MINFER_DECODE_Q8_CTAS : 2) decode_split_kernel(const DecodeArgs a) {
-  constexpr int kStages = stages_of<Q8>();
+// (Q8_0: three thread blocks per SM at 168 registers and a ring of three.  Four blocks at 128 registers spill 90-130
+// bytes and take 0.315 ms where this takes 0.220 ms; a ring of two takes 0.234 ms.)
+__global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(const DecodeArgs a) {
   constexpr int kRowBytes = D * 2;
   constexpr int kTileBytes = kTileKeys * kRowBytes;        // one of K or V, 16-bit
   constexpr int kChunksPerRow = D / 8;                     // 16-byte chunks
@@ -451,7 +447,6 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
 template <int D, bool BF16, bool Q8, bool Paged>
 cudaError_t launch_paged(const DecodeArgs& a, cudaStream_t stream) {
   constexpr int kRaw = Q8 ? kTileKeys * (D / 32) * 34 : kTileKeys * D * 2;
-  constexpr int kStages = stages_of<Q8>();
   constexpr int smem = kWarps * (kStages * 2 * kRaw + (Q8 ? kTileKeys * D * 2 : 0));
   static_assert(smem / kWarps >= 16 * D * 4 + 128, "the per-warp region also holds the fp32 merge buffer");
   static bool attr_done[64] = {};
