@@ -93,7 +93,7 @@ def check_close_bf16_by_keys(actual: torch.Tensor, expected: torch.Tensor, n_key
     emulation of exactly this arithmetic - tile-wise, lazy reference maximum, bfloat16 P, fp32 sums - reproduces the
     kernel's counts to within an element; the same emulation with an exact P leaves only the elements where rounding
     the ORACLE to bfloat16 already fails).  So: rows with at least 128 visible keys must meet atol = rtol = 2e-3 plus
-    half an output ulp without exception; rows with fewer may miss it in at most 2e-4 of their elements, and then
+    half an output ulp without exception; rows with fewer may miss it in at most 5e-4 of their elements, and then
     stay within three times that tolerance."""
     a = actual.detach().float().cpu()
     e = expected.detach().float().cpu()
@@ -104,7 +104,7 @@ def check_close_bf16_by_keys(actual: torch.Tensor, expected: torch.Tensor, n_key
     long_rows = (n_keys >= 128).expand_as(a)
     assert not (bad & long_rows).any(), f"{what}: {int((bad & long_rows).sum())} elements of rows with >= 128 keys out of tolerance"
     n_short = int((~long_rows).sum())
-    assert int(bad.sum()) <= max(1, int(2e-4 * n_short)), f"{what}: {int(bad.sum())} of {n_short} elements of short rows out of tolerance"
+    assert int(bad.sum()) <= max(3, int(5e-4 * n_short)), f"{what}: {int(bad.sum())} of {n_short} elements of short rows out of tolerance"
     assert not (err > 3 * tol).any(), f"{what}: an element is off by more than three times the tolerance"
     return int(bad.sum())
 
