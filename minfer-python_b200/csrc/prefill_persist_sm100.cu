@@ -272,6 +272,13 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   constexpr int kKvEmpty = kKvFull + kStages;
   constexpr int kNumBars = kKvFull + 2 * kStages;
   constexpr uint32_t kTmemCols = 512;
+  // head_dim 64 leaves tensor memory to spare: each slot then has an S region of its own (S0 [0,128), P0 [128,192),
+  // P1 [192,256), O0 [256,320), O1 [320,384), S1 [384,512)), so a slot's next score tile is issued as soon as that
+  // slot has read its previous one, whatever the other slot is doing.  At head_dim 128 the two O regions take the
+  // room and the slots share S [0,128) in turn.
+  constexpr bool kTwoS = (D == 64);
+  constexpr uint32_t kOStride = kTwoS ? 64u : 128u;   // columns between O0 and O1
+  constexpr uint32_t kS1 = kTwoS ? 384u : 0u;         // first column of slot 1's scores
   constexpr uint32_t kIdescS = umma_idesc(kTileM, kTileN, BF16, BF16, false, false);
   // A and B of one MMA share their 16-bit format: a float16 P beside a bfloat16 V (formats 0 and 1 in the two
   // fields) is refused by the hardware as an illegal instruction.
@@ -344,6 +351,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_init(&bars[kPFree + i], 1);
     }
     mbar_init(&bars[kSFree], 128);
+    mbar_init(&bars[kSFree + 1], 128);  // slot 1's own, with two S regions
     for (int i = 0; i < kSchedRing; ++i) {
       mbar_init(&bars[kSched + i], 1);
       mbar_init(&bars[kSchedFree + i], 258);  // the two MMA warps' leaders and the 256 softmax threads
@@ -536,13 +544,14 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           for (int i = 0; i < kDB * 4; ++i) {
             const uint32_t o = (i >> 2) * (kBlockBytes >> 4) + (i & 3) * 2;  // 32 bytes per 16-element k step
             if (leader) {
-              if (i == 0) umma_ss_first(tmem_base, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
-              else umma_ss_acc(tmem_base, desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
+              if (i == 0) umma_ss_first(tmem_base + (s ? kS1 : 0u), desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
+              else umma_ss_acc(tmem_base + (s ? kS1 : 0u), desc(qa + o, kHi), desc(ka + o, kHi), kIdescS);
             }
           }
           if (leader) umma_commit(&bars[kSFull + s]);
         };
         uint32_t s_count = 0;  // score tiles issued over the CTA's lifetime (parity of s_free)
+        [[maybe_unused]] uint32_t s_slot[2] = {0u, 0u};  // the same per slot (two S regions)
         for (int k = 0; ok; ++k) {
           const int id = next_item(k, ok);
           if (!ok) { report_p(a.status, 37); break; }
@@ -573,12 +582,18 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
               if (!ok || !(f & (1u << (2 * s)))) continue;
               // the scores issued last (either slot's) must have been copied out of the S columns
               P_TL(2, t, s * 3 + 0);
-              if (s_count > 0 && !(ok = mbar_wait(&bars[kSFree], (s_count - 1) & 1u, abort_flag))) { report_p(a.status, 38); continue; }
+              if constexpr (kTwoS) {
+                // the slot's own previous scores must have been copied out of its S columns
+                if (s_slot[s] > 0 && !(ok = mbar_wait(&bars[kSFree + s], (s_slot[s] - 1) & 1u, abort_flag))) { report_p(a.status, 38); continue; }
+              } else {
+                if (s_count > 0 && !(ok = mbar_wait(&bars[kSFree], (s_count - 1) & 1u, abort_flag))) { report_p(a.status, 38); continue; }
+              }
               tc_fence_after();
               P_TL(2, t, s * 3 + 1);
               issue_s(s, stk);
               P_TL(2, t, s * 3 + 2);
               ++s_count;
+              ++s_slot[s];
               bool last;
               if constexpr (kMasked) last = ++s_issued[s] == tl.nvis[s];
               else last = t + 1 == tl.nvis[s];
@@ -600,7 +615,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           const int kk1 = (c == kPPieces - 1) ? kTileN / 16 : 2 * kPSplit;
           const uint32_t va = v_lo + st * (kTileBytes >> 4);
           const uint32_t tp = tmem_base + 128 + s * 64;  // P: packed 16-bit pairs, 8 columns per 16 keys
-          const uint32_t to = tmem_base + 256 + s * 128;
+          const uint32_t to = tmem_base + 256 + s * kOStride;
 #pragma unroll
           for (int kk = 0; kk < kTileN / 16; ++kk) {
             if (kk < kk0 || kk >= kk1) continue;
@@ -680,9 +695,9 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int row = tid & 127;
     const int lane = tid & 31;
     const uint32_t t_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tmem_s = tmem_base + t_lane;                 // scores (shared by the two slots)
+    const uint32_t tmem_s = tmem_base + (s ? kS1 : 0u) + t_lane;  // scores (one region shared by the slots, or the slot's own)
     const uint32_t tmem_p = tmem_base + 128 + s * 64 + t_lane;  // packed P
-    const uint32_t tmem_o = tmem_base + 256 + s * 128 + t_lane;
+    const uint32_t tmem_o = tmem_base + 256 + s * kOStride + t_lane;
     const float sl2 = a.scale_log2;
     const int off = a.seq_k - a.seq_q;
     bool ok = true;
@@ -747,7 +762,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tc_wait_ld();
         // the scores are in registers: the S columns may take the next score tile (either slot's)
         tc_fence_before();
-        mbar_arrive(&bars[kSFree]);
+        mbar_arrive(&bars[kSFree + (kTwoS ? s : 0)]);
         P_TL(s, j, 2);
         P_ACC(acc_c = clock64(); acc_ld += acc_c - acc_c2);
 
