@@ -68,8 +68,27 @@ def flash_attn_decode(kerns, args, dtype):
     return lambda: kerns.flash_attn_decode(q, kc, vc, lens, out)
 
 
+def flash_attn_decode_q8(kerns, args, dtype):
+    """the same decode over a GGML Q8_0 cache (random int8 values, every block scale 2^-7)"""
+    B, H, Hkv, D, Lmax = args.batch, args.heads, args.kv_heads, args.head_dim, args.seq
+    g = torch.Generator().manual_seed(args.seed)
+    lens = torch.randint(max(1, Lmax // 16), Lmax + 1, (B,), generator=g, dtype=torch.int32)
+    print(f"decode q8: sum(lens) = {int(lens.sum())}, live KV bytes = {int(lens.sum()) * Hkv * (D // 32) * 34 * 2}")
+    lens = lens.cuda()
+    q = torch.randn((B, H, 1, D), dtype=dtype, device="cuda")
+    caches = []
+    for _ in range(2):
+        c = torch.randint(0, 256, (B, Hkv, Lmax, D // 32, 34), dtype=torch.uint8, device="cuda")
+        c[..., 0] = 0x00
+        c[..., 1] = 0x20   # fp16 0x2000 = 2^-7
+        caches.append(c.view(B, Hkv, Lmax, D // 32 * 34))
+    out = torch.zeros_like(q)
+    return lambda: kerns.flash_attn_decode_q8(q, caches[0], caches[1], lens, out)
+
+
 if __name__ == "__main__":
-    KERNELS = {"flash_attn": flash_attn, "flash_attn_causal": flash_attn_causal, "flash_attn_decode": flash_attn_decode}
+    KERNELS = {"flash_attn": flash_attn, "flash_attn_causal": flash_attn_causal, "flash_attn_decode": flash_attn_decode,
+               "flash_attn_decode_q8": flash_attn_decode_q8}
     parser = argparse.ArgumentParser()
     parser.add_argument("--backend", choices=["torch_ext"], default="torch_ext")
     parser.add_argument("--kernel", choices=sorted(KERNELS), required=True)

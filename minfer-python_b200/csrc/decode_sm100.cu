@@ -18,10 +18,16 @@
 // Q8 = true: the caches hold GGML Q8_0 blocks (32 int8 + one fp16 scale, 34 bytes;
 // the reference's block_q8_0, src/minfer/kernels/torch_ext/csrc/common/types.hpp:141-146).
 // The raw bytes of a 16-key tile are contiguous in the cache and ride the same
-// cp.async ring; each warp then dequantises its tile into a 16-bit tile in
-// shared memory, value by value exactly as the reference's dequant_row_q8_0<half>
-// does ((half)(q * d), csrc/quants/impl.cpp:1153-1166), and the arithmetic above
-// runs unchanged.  Cache bytes per key drop from 4 D to 2.125 D.
+// cp.async ring; every lane then builds its tensor-core B fragments straight from
+// the raw rows in shared memory - two int8 dropped into the mantissas of a pair of
+// halves, the bias subtracted, one multiply by the block's scale - so each value
+// is (16-bit type)(q * d), rounded once, exactly as the reference's
+// dequant_row_q8_0<half> produces it (csrc/quants/impl.cpp:1153-1166), and no
+// 16-bit copy of the tile is ever written.  K keeps the key and dimension order of
+// the 16-bit path, so the scores are the same bits; for V a lane takes four
+// consecutive dimensions of each block (the output columns come out permuted
+// inside a block and are put back in the merge), which leaves every sum over the
+// keys as it was.  Cache bytes per key drop from 4 D to 2.125 D.
 //
 // Kernel 2 (decode_combine_kernel): grid (n_heads, batch) merges the partials
 // of the ceil(len / chunk) splits of a sequence and writes the 16-bit output.
@@ -41,6 +47,13 @@ namespace {
 
 constexpr int kWarps = 4;
 constexpr int kStages = 3;
+// Q8_0: thread blocks per SM and ring depth (raw tiles are about half the bytes of 16-bit ones)
+#ifndef MINFER_ATTN_Q8_CTAS
+#define MINFER_ATTN_Q8_CTAS 3
+#endif
+#ifndef MINFER_ATTN_Q8_STAGES
+#define MINFER_ATTN_Q8_STAGES 4
+#endif
 constexpr int kTileKeys = 16;
 
 // kept out of line: the error path must not cost the streaming loop registers
@@ -59,60 +72,48 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
   else return row * 128 + (((chunk ^ row) & 7) << 4);
 }
 
-// Eight values of one Q8_0 block (quarter `part` of its 32) -> eight 16-bit values at dst.
-// Each value is (16-bit type)(q * d) with d the block's fp16 scale: the product of an 8-bit integer
-// and an fp16 is exact in fp32, so this is one rounding, as in the reference's dequant_row_q8_0.
-// Dead rows (beyond the sequence) become zeros so that no stale byte can turn into Inf/NaN.
+// Two int8 of a Q8_0 block -> a pair of 16-bit values (q * d), rounded once.  `src` holds the bytes already
+// XORed with 0x80 (q + 128 as an unsigned byte); I0 / I1 pick the bytes of the low / high value.
+//   float16: the byte dropped into the mantissa of the half 1024.0 reads 1024 + 128 + q; subtracting 1152 leaves q
+//   exactly and one half multiply by d rounds once, as (half)(q * d) does.  No conversion instruction.
+//   bfloat16: the same in fp32 (2^23 + 128 + q), where q * d is exact, then one rounding to bfloat16.
 template <bool BF16>
-__device__ __forceinline__ void dequant8(const uint8_t* block, int part, bool live, uint8_t* dst) {
-  uint4 out = make_uint4(0u, 0u, 0u, 0u);
-  if (live) {
-    const uint16_t* q16 = reinterpret_cast<const uint16_t*>(block + 2 + part * 8);  // 2-byte aligned
-    const uint32_t w0 = static_cast<uint32_t>(q16[0]) | (static_cast<uint32_t>(q16[1]) << 16);
-    const uint32_t w1 = static_cast<uint32_t>(q16[2]) | (static_cast<uint32_t>(q16[3]) << 16);
-    if constexpr (BF16) {
-      const float d = __half2float(*reinterpret_cast<const __half*>(block));
-      const uint32_t w[2] = {w0, w1};
-      uint32_t o[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t two = (w[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu;
-        o[i] = pack2<true>(static_cast<float>(static_cast<int8_t>(two & 0xFFu)) * d,
-                           static_cast<float>(static_cast<int8_t>(two >> 8)) * d);
-      }
-      out = make_uint4(o[0], o[1], o[2], o[3]);
-    } else {
-      // No conversion instructions: the byte q + 128 dropped into the mantissa of the half 1024.0
-      // reads as 1024 + 128 + q; subtracting 1152 leaves q exactly, and one half multiply by d
-      // rounds once, as (half)(q * d) does.
-      const uint32_t dbits = *reinterpret_cast<const uint16_t*>(block);
-      const __half2 d2 = *reinterpret_cast<const __half2*>(&(const uint32_t&)(dbits | (dbits << 16)));
-      const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
-      const uint32_t x[2] = {w0 ^ 0x80808080u, w1 ^ 0x80808080u};
-      uint32_t o[4];
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const uint32_t lo = __byte_perm(x[i], 0x64646464u, 0x5140);  // bytes 0,1 -> two halves 0x64:b
-        const uint32_t hi = __byte_perm(x[i], 0x64646464u, 0x5342);  // bytes 2,3
-        const __half2 qlo = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias);
-        const __half2 qhi = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
-        const __half2 vlo = __hmul2(qlo, d2);
-        const __half2 vhi = __hmul2(qhi, d2);
-        o[2 * i] = *reinterpret_cast<const uint32_t*>(&vlo);
-        o[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&vhi);
-      }
-      out = make_uint4(o[0], o[1], o[2], o[3]);
-    }
+struct Q8Scale { uint32_t h2; };          // two fp16 scales (low value's, high value's)
+template <>
+struct Q8Scale<true> { float2 f2; };
+template <bool BF16>
+__device__ __forceinline__ Q8Scale<BF16> q8_scale(uint32_t d_lo, uint32_t d_hi) {  // fp16 bit patterns
+  Q8Scale<BF16> r;
+  if constexpr (BF16) {
+    r.f2 = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(d_lo))),
+                       __half2float(__ushort_as_half(static_cast<unsigned short>(d_hi))));
+  } else {
+    r.h2 = d_lo | (d_hi << 16);
   }
-  *reinterpret_cast<uint4*>(dst) = out;
+  return r;
+}
+template <bool BF16, int I0, int I1>
+__device__ __forceinline__ uint32_t q8_pair(uint32_t src, const Q8Scale<BF16>& d) {
+  if constexpr (BF16) {
+    const float lo = __uint_as_float(__byte_perm(src, 0x4B000000u, 0x7650 | I0));
+    const float hi = __uint_as_float(__byte_perm(src, 0x4B000000u, 0x7650 | I1));
+    const float2 q = __fadd2_rn(make_float2(lo, hi), make_float2(-8388736.f, -8388736.f));
+    const float2 v = __fmul2_rn(q, d.f2);
+    return pack2<true>(v.x, v.y);
+  } else {
+    const uint32_t x = __byte_perm(src, 0x64646464u, 0x5040 | I0 | (I1 << 8));
+    const uint32_t bias = 0x64806480u;  // 1152.0 twice
+    const __half2 q = __hsub2(*reinterpret_cast<const __half2*>(&x), *reinterpret_cast<const __half2*>(&bias));
+    const __half2 v = __hmul2(q, *reinterpret_cast<const __half2*>(&d.h2));
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
 }
 
 // Paged: the caches are pools of pages reached through a.block_table (a separate instantiation, so that the
 // contiguous form keeps its registers).
 template <int D, bool BF16, bool Q8, bool Paged>
-// (Q8_0: three thread blocks per SM at 168 registers and a ring of three.  Four blocks at 128 registers spill 90-130
-// bytes and take 0.315 ms where this takes 0.220 ms; a ring of two takes 0.234 ms.)
-__global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(const DecodeArgs a) {
+__global__ void __launch_bounds__(kWarps * 32, Q8 ? MINFER_ATTN_Q8_CTAS : 2) decode_split_kernel(const DecodeArgs a) {
+  constexpr int kSt = Q8 ? MINFER_ATTN_Q8_STAGES : kStages;
   constexpr int kRowBytes = D * 2;
   constexpr int kTileBytes = kTileKeys * kRowBytes;        // one of K or V, 16-bit
   constexpr int kChunksPerRow = D / 8;                     // 16-byte chunks
@@ -122,9 +123,8 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
   constexpr int kQTileBytes = kTileKeys * kQRowBytes;      // 2176 (D=128) / 1088 (D=64): multiples of 16
   constexpr int kQChunks = kQTileBytes / 16;
   constexpr int kQLoadsPerLane = (kQChunks + 31) / 32;
-  // per warp: the ring of raw tiles, plus (Q8) one 16-bit tile that holds the dequantised K, then V
-  constexpr int kRingBytes = kStages * 2 * (Q8 ? kQTileBytes : kTileBytes);
-  constexpr int kWarpBytes = kRingBytes + (Q8 ? kTileBytes : 0);
+  // per warp: the ring of raw tiles
+  constexpr int kWarpBytes = kSt * 2 * (Q8 ? kQTileBytes : kTileBytes);
 
   extern __shared__ __align__(128) uint8_t smem[];
 
@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
   };
   const size_t row_stride_bytes = 2 * static_cast<size_t>(a.kv_stride[2]);  // 16-bit caches
 
-  auto issue_tile = [&](int i) {  // i-th tile of this warp -> stage i % kStages
+  auto issue_tile = [&](int i) {  // i-th tile of this warp -> stage i % kSt
     if (i < nt_w) {
       const int key0 = c0 + (warp + i * kWarps) * kTileKeys;
       const size_t toff = tile_offset(key0);
@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
         // strides of a Q8_0 cache are in bytes; rows are contiguous
         const uint8_t* kq = reinterpret_cast<const uint8_t*>(a.k) + toff;
         const uint8_t* vq = reinterpret_cast<const uint8_t*>(a.v) + toff;
-        uint8_t* dst_k = wsm + (i % kStages) * 2 * kQTileBytes;
+        uint8_t* dst_k = wsm + (i % kSt) * 2 * kQTileBytes;
         uint8_t* dst_v = dst_k + kQTileBytes;
         // bytes of live rows in this tile (rows beyond the sequence are neither read nor used)
         const int live = min(kTileKeys, c1 - key0) * kQRowBytes;
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
         cp_async_commit();
         return;
       }
-      uint8_t* dst_k = wsm + (i % kStages) * 2 * kTileBytes;
+      uint8_t* dst_k = wsm + (i % kSt) * 2 * kTileBytes;
       uint8_t* dst_v = dst_k + kTileBytes;
 #pragma unroll
       for (int t = 0; t < kLoadsPerLane; ++t) {
@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
   };
 
 #pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) issue_tile(s);
+  for (int s = 0; s < kSt - 1; ++s) issue_tile(s);
 
   // ---- Q fragments: rows = query heads of this kv head (zero beyond group) ----
   const int g0 = lane >> 2;
@@ -242,48 +242,47 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
   const int lm_r = lane & 7;
 
   for (int i = 0; i < nt_w; ++i) {
-    cp_async_wait<kStages - 2>();
+    cp_async_wait<kSt - 2>();
     __syncwarp();
-    issue_tile(i + kStages - 1);
+    issue_tile(i + kSt - 1);
 
     const int key0 = c0 + (warp + i * kWarps) * kTileKeys;
-    uint32_t sk, sv;
-    // Q8: dequantise K (and later V) of the raw tile into the warp's one 16-bit tile, same swizzle
-    // as the 16-bit path, so the ldmatrix / mma code below is shared
-    const uint8_t* raw_k = wsm + (Q8 ? (i % kStages) * 2 * kQTileBytes : 0);
-    const int live_rows = min(kTileKeys, c1 - key0);
-    auto dequant_tile = [&](const uint8_t* raw) {
-      uint8_t* deq = wsm + kRingBytes;
-      __syncwarp();  // earlier ldmatrix reads of the tile are done
-#pragma unroll
-      for (int t = 0; t < kLoadsPerLane; ++t) {
-        const int idx = t * 32 + lane;
-        const int row = idx / kChunksPerRow;
-        const int chunk = idx % kChunksPerRow;
-        // the block holding elements 8*chunk .. 8*chunk+7 of the row
-        dequant8<BF16>(raw + row * kQRowBytes + (chunk >> 2) * 34, chunk & 3, row < live_rows, deq + swz<D>(row, chunk));
-      }
-      __syncwarp();
-    };
-    if constexpr (Q8) {
-      dequant_tile(raw_k);
-      sk = wsm_u32 + kRingBytes;
-      sv = sk;
-    } else {
-      sk = wsm_u32 + (i % kStages) * 2 * kTileBytes;
-      sv = sk + kTileBytes;
-    }
-
     // ---- S[16 heads x 16 keys] = Q K^T ----
     float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    [[maybe_unused]] const uint8_t* raw_k = wsm + (i % kSt) * 2 * kQTileBytes;  // Q8: this tile's raw K rows, then V
+    [[maybe_unused]] uint32_t sv = 0;
+    if constexpr (Q8) {
+      // B fragments from the raw rows: lane (g0, tq) holds keys g0 / g0 + 8 and, per 16-dimension step, the pairs
+      // at 2 tq and 2 tq + 8 - two-byte loads (the blocks' 34 bytes leave nothing better aligned), the four lanes
+      // of a key reading 8 consecutive bytes.  Rows beyond the chunk were zero-filled by the copy (scale 0).
 #pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      uint32_t r0, r1, r2, r3;
-      const int key = (lm_mi >> 1) * 8 + lm_r;
-      const int chunk = 2 * ks + (lm_mi & 1);
-      ldmatrix_x4(sk + swz<D>(key, chunk), r0, r1, r2, r3);
-      mma_16816<BF16>(sacc[0], qf[ks], r0, r1);
-      mma_16816<BF16>(sacc[1], qf[ks], r2, r3);
+      for (int blk = 0; blk < D / 32; ++blk) {
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+          const uint8_t* bp = raw_k + (g0 + 8 * nb) * kQRowBytes + blk * 34;
+          const uint32_t db = *reinterpret_cast<const uint16_t*>(bp);
+          const Q8Scale<BF16> d = q8_scale<BF16>(db, db);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t u0 = *reinterpret_cast<const uint16_t*>(bp + 2 + 16 * h + 2 * tq);
+            const uint32_t u1 = *reinterpret_cast<const uint16_t*>(bp + 2 + 16 * h + 8 + 2 * tq);
+            mma_16816<BF16>(sacc[nb], qf[2 * blk + h], q8_pair<BF16, 0, 1>(u0 ^ 0x8080u, d),
+                            q8_pair<BF16, 0, 1>(u1 ^ 0x8080u, d));
+          }
+        }
+      }
+    } else {
+      const uint32_t sk = wsm_u32 + (i % kSt) * 2 * kTileBytes;
+      sv = sk + kTileBytes;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t r0, r1, r2, r3;
+        const int key = (lm_mi >> 1) * 8 + lm_r;
+        const int chunk = 2 * ks + (lm_mi & 1);
+        ldmatrix_x4(sk + swz<D>(key, chunk), r0, r1, r2, r3);
+        mma_16816<BF16>(sacc[0], qf[ks], r0, r1);
+        mma_16816<BF16>(sacc[1], qf[ks], r2, r3);
+      }
     }
 
     // ---- scale, mask the ragged end, online softmax ----
@@ -333,15 +332,52 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
     pa[3] = pack2<BF16>(sacc[1][2], sacc[1][3]);
 
     // ---- O[16 heads x D] += P V ----
-    if constexpr (Q8) dequant_tile(raw_k + kQTileBytes);
+    if constexpr (Q8) {
+      // B fragments pair two keys per register: lane (g0, tq) reads, for keys 2 tq, 2 tq + 1, 2 tq + 8, 2 tq + 9, the
+      // four bytes at dimensions 4 g0 .. 4 g0 + 3 of every block, interleaves the rows pairwise and converts.
+      // Output tile 4 blk + j then holds, in column c, dimension 32 blk + 4 c + j (see q8_dim below).
+      const uint8_t* rv = raw_k + kQTileBytes + (2 * tq) * kQRowBytes + 4 * g0;
+      // The copy zero-fills whole 16-byte pieces beyond the chunk, so the first row past the end can hold a few
+      // real cache bytes, a scale among them: rows past the end get scale 0 (their weights are 0, and 0 * 0 = 0
+      // whatever the cache holds there).
+      uint32_t row_ok[4];
 #pragma unroll
-    for (int dn = 0; dn < D / 16; ++dn) {
-      uint32_t r0, r1, r2, r3;
-      const int key = (lm_mi & 1) * 8 + lm_r;
-      const int chunk = 2 * dn + (lm_mi >> 1);
-      ldmatrix_x4_trans(sv + swz<D>(key, chunk), r0, r1, r2, r3);
-      mma_16816<BF16>(oacc[2 * dn], pa, r0, r1);
-      mma_16816<BF16>(oacc[2 * dn + 1], pa, r2, r3);
+      for (int r = 0; r < 4; ++r) row_ok[r] = (key0 + 2 * tq + (r & 1) + 8 * (r >> 1) < c1) ? 0xFFFFu : 0u;
+#pragma unroll
+      for (int blk = 0; blk < D / 32; ++blk) {
+        uint32_t x[4], dsc[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const uint8_t* bp = rv + ((r & 1) + 8 * (r >> 1)) * kQRowBytes + blk * 34;
+          dsc[r] = *reinterpret_cast<const uint16_t*>(bp - 4 * g0) & row_ok[r];
+          uint32_t w;
+          if (blk & 1) {  // 34 blk + 2 is a multiple of 4 for odd blocks
+            w = *reinterpret_cast<const uint32_t*>(bp + 2);
+          } else {
+            w = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(bp + 2)) |
+                (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(bp + 4)) << 16);
+          }
+          x[r] = w ^ 0x80808080u;
+        }
+        const Q8Scale<BF16> d01 = q8_scale<BF16>(dsc[0], dsc[1]);
+        const Q8Scale<BF16> d23 = q8_scale<BF16>(dsc[2], dsc[3]);
+        const uint32_t lo01 = __byte_perm(x[0], x[1], 0x5140), hi01 = __byte_perm(x[0], x[1], 0x7362);
+        const uint32_t lo23 = __byte_perm(x[2], x[3], 0x5140), hi23 = __byte_perm(x[2], x[3], 0x7362);
+        mma_16816<BF16>(oacc[4 * blk + 0], pa, q8_pair<BF16, 0, 1>(lo01, d01), q8_pair<BF16, 0, 1>(lo23, d23));
+        mma_16816<BF16>(oacc[4 * blk + 1], pa, q8_pair<BF16, 2, 3>(lo01, d01), q8_pair<BF16, 2, 3>(lo23, d23));
+        mma_16816<BF16>(oacc[4 * blk + 2], pa, q8_pair<BF16, 0, 1>(hi01, d01), q8_pair<BF16, 0, 1>(hi23, d23));
+        mma_16816<BF16>(oacc[4 * blk + 3], pa, q8_pair<BF16, 2, 3>(hi01, d01), q8_pair<BF16, 2, 3>(hi23, d23));
+      }
+    } else {
+#pragma unroll
+      for (int dn = 0; dn < D / 16; ++dn) {
+        uint32_t r0, r1, r2, r3;
+        const int key = (lm_mi & 1) * 8 + lm_r;
+        const int chunk = 2 * dn + (lm_mi >> 1);
+        ldmatrix_x4_trans(sv + swz<D>(key, chunk), r0, r1, r2, r3);
+        mma_16816<BF16>(oacc[2 * dn], pa, r0, r1);
+        mma_16816<BF16>(oacc[2 * dn + 1], pa, r2, r3);
+      }
     }
   }
   cp_async_wait<0>();
@@ -362,8 +398,16 @@ __global__ void __launch_bounds__(kWarps * 32, Q8 ? 3 : 2) decode_split_kernel(c
     const int g = g0 + 8 * r;
     if (g < a.group) {
 #pragma unroll
-      for (int n = 0; n < D / 8; ++n)
-        *reinterpret_cast<float2*>(&mo[g * D + n * 8 + tq * 2]) = make_float2(oacc[n][2 * r], oacc[n][2 * r + 1]);
+      for (int n = 0; n < D / 8; ++n) {
+        if constexpr (Q8) {
+          // column c of output tile 4 blk + j is dimension 32 blk + 4 c + j; this lane holds columns 2 tq, 2 tq + 1
+          const int d0 = 32 * (n >> 2) + 8 * tq + (n & 3);
+          mo[g * D + d0] = oacc[n][2 * r];
+          mo[g * D + d0 + 4] = oacc[n][2 * r + 1];
+        } else {
+          *reinterpret_cast<float2*>(&mo[g * D + n * 8 + tq * 2]) = make_float2(oacc[n][2 * r], oacc[n][2 * r + 1]);
+        }
+      }
       if (tq == 0) {
         mml[g * 2] = m_run[r];
         mml[g * 2 + 1] = l_run[r];
@@ -447,7 +491,7 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
 template <int D, bool BF16, bool Q8, bool Paged>
 cudaError_t launch_paged(const DecodeArgs& a, cudaStream_t stream) {
   constexpr int kRaw = Q8 ? kTileKeys * (D / 32) * 34 : kTileKeys * D * 2;
-  constexpr int smem = kWarps * (kStages * 2 * kRaw + (Q8 ? kTileKeys * D * 2 : 0));
+  constexpr int smem = kWarps * (Q8 ? MINFER_ATTN_Q8_STAGES : kStages) * 2 * kRaw;
   static_assert(smem / kWarps >= 16 * D * 4 + 128, "the per-warp region also holds the fp32 merge buffer");
   static bool attr_done[64] = {};
   int dev = 0;

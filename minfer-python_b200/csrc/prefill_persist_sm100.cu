@@ -272,11 +272,16 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   constexpr int kKvEmpty = kKvFull + kStages;
   constexpr int kNumBars = kKvFull + 2 * kStages;
   constexpr uint32_t kTmemCols = 512;
-  // head_dim 64 leaves tensor memory to spare: each slot then has an S region of its own (S0 [0,128), P0 [128,192),
-  // P1 [192,256), O0 [256,320), O1 [320,384), S1 [384,512)), so a slot's next score tile is issued as soon as that
-  // slot has read its previous one, whatever the other slot is doing.  At head_dim 128 the two O regions take the
-  // room and the slots share S [0,128) in turn.
-  constexpr bool kTwoS = (D == 64);
+  // head_dim 64 leaves tensor memory to spare, so each slot could have an S region of its own (S0 [0,128),
+  // P0 [128,192), P1 [192,256), O0 [256,320), O1 [320,384), S1 [384,512)) and its next score tile issued as soon as
+  // that slot has read its previous one, whatever the other slot is doing (MINFER_ATTN_D64_TWO_S=1).  Measured
+  // against the shared region, interleaved in one process: 767 vs 806 TFLOP/s at B=2 L=8192, 234 vs 237 at B=8
+  // L=512 (bursts), 728 vs 778 and 247 vs 256 sustained: the alternation that the shared region forces keeps the
+  // two slots' softmax half a period apart, which is what lets them share the special-function unit.  Off.
+#ifndef MINFER_ATTN_D64_TWO_S
+#define MINFER_ATTN_D64_TWO_S 0
+#endif
+  constexpr bool kTwoS = (D == 64) && MINFER_ATTN_D64_TWO_S != 0;
   constexpr uint32_t kOStride = kTwoS ? 64u : 128u;   // columns between O0 and O1
   constexpr uint32_t kS1 = kTwoS ? 384u : 0u;         // first column of slot 1's scores
   constexpr uint32_t kIdescS = umma_idesc(kTileM, kTileN, BF16, BF16, false, false);
