@@ -5,6 +5,8 @@
 #include "../../include/minfer_attn.h"
 #include "attn_internal.h"
 
+#include <atomic>
+
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -32,13 +34,17 @@ EncodeTiledFn get_encode_fn() {
 
 // Is the current device compute capability 10.x?  Cached per device.
 int check_device() {
-  static int cached[64] = {};  // 0 unknown, 1 ok, 2 wrong arch
+  // 0 unknown, 1 ok, 2 wrong arch; atomics: several host threads may drive different devices
+  static std::atomic<int> cached[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return MINFER_ATTN_ECUDA;
-  if (dev < 64 && cached[dev] != 0) return cached[dev] == 1 ? MINFER_ATTN_OK : MINFER_ATTN_ENODEVICE;
+  if (dev < 64) {
+    const int c = cached[dev].load(std::memory_order_acquire);
+    if (c != 0) return c == 1 ? MINFER_ATTN_OK : MINFER_ATTN_ENODEVICE;
+  }
   int major = 0;
   if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return MINFER_ATTN_ECUDA;
-  if (dev < 64) cached[dev] = (major == 10) ? 1 : 2;
+  if (dev < 64) cached[dev].store((major == 10) ? 1 : 2, std::memory_order_release);
   return major == 10 ? MINFER_ATTN_OK : MINFER_ATTN_ENODEVICE;
 }
 

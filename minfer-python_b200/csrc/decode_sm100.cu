@@ -38,6 +38,7 @@
 #include "attn_internal.h"
 #include "ptx.cuh"
 
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -493,14 +494,14 @@ cudaError_t launch_paged(const DecodeArgs& a, cudaStream_t stream) {
   constexpr int kRaw = Q8 ? kTileKeys * (D / 32) * 34 : kTileKeys * D * 2;
   constexpr int smem = kWarps * (Q8 ? MINFER_ATTN_Q8_STAGES : kStages) * 2 * kRaw;
   static_assert(smem / kWarps >= 16 * D * 4 + 128, "the per-warp region also holds the fp32 merge buffer");
-  static bool attr_done[64] = {};
+  static std::atomic<bool> attr_done[64] = {};  // set-once flags; the attribute call itself is idempotent
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  if (dev < 64 && !attr_done[dev]) {
+  if (dev < 64 && !attr_done[dev].load(std::memory_order_acquire)) {
     e = cudaFuncSetAttribute(decode_split_kernel<D, BF16, Q8, Paged>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    attr_done[dev] = true;
+    attr_done[dev].store(true, std::memory_order_release);
   }
   dim3 grid(a.n_split, a.n_kv_heads, a.batch);
   decode_split_kernel<D, BF16, Q8, Paged><<<grid, kWarps * 32, smem, stream>>>(a);

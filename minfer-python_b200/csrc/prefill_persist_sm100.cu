@@ -47,6 +47,8 @@
 #include "attn_internal.h"
 #include "ptx.cuh"
 
+#include <atomic>
+
 namespace minfer_attn {
 
 namespace {
@@ -977,26 +979,27 @@ cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, con
   constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 8 * kEpiBytes + 512 +
                           (kMasked ? kMaskRing * (kMaxTiles / 8) * 4 : 0) + 1024;
   static_assert(smem <= 232448, "shared memory per CTA");
-  static bool attr_done[64] = {};
-  static int sm_count[64] = {};
+  // set once per device (0 = not yet); atomic because several host threads may drive different devices
+  static std::atomic<int> sm_count[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev >= 64) return cudaErrorInvalidDevice;
-  if (!attr_done[dev]) {
+  int sms = sm_count[dev].load(std::memory_order_acquire);
+  if (sms == 0) {
     e = cudaFuncSetAttribute(prefill_persist_kernel<D, BF16, kMasked>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
-    attr_done[dev] = true;
+    sm_count[dev].store(sms, std::memory_order_release);
   }
   const int n_qt = (a.seq_q + kTileM - 1) / kTileM;
   a.items_x = a.pair_heads ? n_qt : (n_qt + 1) / 2;
   a.items_y = a.pair_heads ? a.n_heads / 2 : a.n_heads;
   const long long n_items = static_cast<long long>(a.items_x) * a.items_y * a.batch;
   if (n_items > 0x7FFFFFFF) return cudaErrorInvalidValue;
-  int ctas = sm_count[dev];
+  int ctas = sms;
   if (a.max_ctas > 0 && a.max_ctas < ctas) ctas = a.max_ctas;
   const int grid = static_cast<int>(n_items < ctas ? n_items : ctas);
   // Order of the dynamically claimed items: globally longest-first while all K/V of the call fit
