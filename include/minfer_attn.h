@@ -284,7 +284,7 @@ typedef struct MinferRopeParams {
   int64_t q_stride[3];
   int64_t kv_stride[3];
   int64_t cache_stride[3];
-  int32_t batch;
+  int32_t batch;          /* batch * seq * head_dim / 8 must stay below 2^31 - 64 (EINVAL otherwise) */
   int32_t seq;
   int32_t n_heads;
   int32_t n_kv_heads;

@@ -86,9 +86,22 @@ def flash_attn_decode_q8(kerns, args, dtype):
     return lambda: kerns.flash_attn_decode_q8(q, caches[0], caches[1], lens, out)
 
 
+def rope_kv_append(kerns, args, dtype):
+    """interleaved RoPE of q and k fused with the append of k and v to a [B, Hkv, 2*seq, D] cache"""
+    B, H, Hkv, D, L = args.batch, args.heads, args.kv_heads, args.head_dim, args.seq
+    q = torch.randn((B, L, H, D), dtype=dtype, device="cuda")
+    k = torch.randn((B, L, Hkv, D), dtype=dtype, device="cuda")
+    v = torch.randn((B, L, Hkv, D), dtype=dtype, device="cuda")
+    kc = torch.zeros((B, Hkv, 2 * L, D), dtype=dtype, device="cuda")
+    vc = torch.zeros_like(kc)
+    start = torch.zeros(B, dtype=torch.int32, device="cuda")
+    print(f"rope_kv_append: bytes = {2 * B * L * D * (2 * H + 4 * Hkv)}")
+    return lambda: kerns.rope_kv_append(D, 500000.0, 0, q, k, v, kc, vc, start)
+
+
 if __name__ == "__main__":
     KERNELS = {"flash_attn": flash_attn, "flash_attn_causal": flash_attn_causal, "flash_attn_decode": flash_attn_decode,
-               "flash_attn_decode_q8": flash_attn_decode_q8}
+               "flash_attn_decode_q8": flash_attn_decode_q8, "rope_kv_append": rope_kv_append}
     parser = argparse.ArgumentParser()
     parser.add_argument("--backend", choices=["torch_ext"], default="torch_ext")
     parser.add_argument("--kernel", choices=sorted(KERNELS), required=True)

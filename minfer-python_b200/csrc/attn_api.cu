@@ -274,6 +274,8 @@ int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {
   if (p == nullptr) return MINFER_ATTN_EINVAL;
   if (p->q == nullptr && p->k == nullptr && p->v == nullptr) return MINFER_ATTN_EINVAL;
   if (p->batch <= 0 || p->seq <= 0 || p->head_dim <= 0 || p->head_dim % 8 != 0) return MINFER_ATTN_EINVAL;
+  // the kernel indexes (token, 16-byte chunk) pairs in 32 bits
+  if (static_cast<long long>(p->batch) * p->seq * (p->head_dim / 8) >= (1ll << 31) - 64) return MINFER_ATTN_EINVAL;
   if (p->dtype != MINFER_ATTN_F16 && p->dtype != MINFER_ATTN_BF16) return MINFER_ATTN_EINVAL;
   if (p->style != 0 && p->style != 1) return MINFER_ATTN_EINVAL;
   if (p->rotary_dim < 0 || p->rotary_dim > p->head_dim || p->rotary_dim % (p->style == 1 ? 16 : 8) != 0)

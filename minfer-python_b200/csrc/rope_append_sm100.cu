@@ -22,10 +22,13 @@
 // (csrc/quants/impl.cpp:1169-1193): d = max|x| / 127, q = roundf(x / d), 32 values per block.
 // The four threads that own one block's four chunks agree on the maximum with two shuffles.
 //
-// Thread mapping: a thread owns one token and one 16-byte chunk of head_dim
-// (neox: the chunk and its partner chunk) and walks a slice of the token's rows
-// (query heads, k heads, v heads), four rows at a time with all loads issued
-// first; the sin/cos of its 4 (8) angles are computed once per thread.
+// Thread mapping: a (token, 16-byte chunk of head_dim) pair (neox: the chunk and its
+// partner chunk) is served by four threads of a block, one per slice of the token's
+// rows (query heads, k heads, v heads; more slices over gridDim.y for small calls).
+// The four compute one (two) of the pair's 4 (8) angles each - powf and sincosf are
+// some 250 instructions per angle, which made the kernel instruction-bound when every
+// thread computed all of them - and share them through shared memory; then each walks
+// its rows four at a time with all loads issued first.
 #include "../../include/minfer_attn.h"
 #include "attn_internal.h"
 
@@ -101,15 +104,34 @@ __device__ __forceinline__ void round16(float (&x)[8]) {
 }
 
 // kNeox = false: interleaved pairs; true: two halves.
+// The kernel waits on its loads more than on anything else, so residency decides: four 256-thread blocks per SM
+// (64 registers) with four rows in flight per thread take 77 us on a prefill-sized call (B=4, L=4096, 32/8 heads,
+// D=128) where three blocks (80 registers, no spills) take 82 and two blocks with six rows 93; the two-halves form
+// holds twice the data per row and keeps its registers with two rows per step (83 us; four rows spill: 125).
+#ifndef MINFER_ATTN_ROPE_MINBLOCKS
+#define MINFER_ATTN_ROPE_MINBLOCKS 4
+#endif
+constexpr int kRopePairs = 64;    // (token, chunk) pairs per 256-thread block
+constexpr int kRopeSlices = 4;    // threads per pair = row slices inside a block (warp-uniform: two warps each)
+
 template <bool BF16, bool kNeox>
-__global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
+__global__ void __launch_bounds__(kRopePairs * kRopeSlices, MINFER_ATTN_ROPE_MINBLOCKS) rope_append_kernel(const RopeArgs a) {
+  constexpr int kRopeRows = kNeox ? 2 : 4;           // rows a thread loads before it computes
+  __shared__ __align__(16) float s_cs[kRopePairs][8];
+  __shared__ __align__(16) float s_sn[kRopePairs][8];
   const int chunks = a.head_dim / 8;                 // 16-byte chunks per head row
   const int rot_chunks = a.rotary_dim / 8;
   const int work_chunks = kNeox ? chunks - rot_chunks / 2 : chunks;  // neox: a thread takes a chunk and its partner
-  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const long long token = gid / work_chunks;
-  if (token >= static_cast<long long>(a.batch) * a.seq) return;
-  int c = static_cast<int>(gid % work_chunks);
+  const int pair = static_cast<int>(threadIdx.x) % kRopePairs;
+  const int slice_in = static_cast<int>(threadIdx.x) / kRopePairs;
+  // 32-bit index arithmetic (the launcher refuses calls with 2^31 pairs or more): a 64-bit division is some
+  // hundred instructions, and there were four of them per thread
+  const unsigned gid = blockIdx.x * static_cast<unsigned>(kRopePairs) + static_cast<unsigned>(pair);
+  const unsigned n_tokens = static_cast<unsigned>(a.batch) * static_cast<unsigned>(a.seq);
+  const unsigned tok_raw = gid / static_cast<unsigned>(work_chunks);
+  const bool valid = tok_raw < n_tokens;              // the last block may hold pairs beyond the last token
+  const unsigned token = valid ? tok_raw : n_tokens - 1;
+  int c = static_cast<int>(gid - tok_raw * static_cast<unsigned>(work_chunks));
   // neox work item c: c < rot_chunks/2 -> rotated pair (c, c + rot_chunks/2); else passthrough chunk c + rot_chunks/2
   int c2 = -1;
   bool rotate;
@@ -124,8 +146,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
   } else {
     rotate = c < rot_chunks;
   }
-  const int b = static_cast<int>(token / a.seq);
-  const int l = static_cast<int>(token % a.seq);
+  const int b = static_cast<int>(token / static_cast<unsigned>(a.seq));
+  const int l = static_cast<int>(token - static_cast<unsigned>(b) * static_cast<unsigned>(a.seq));
   const int pos = (a.start ? a.start[b] : a.start_pos) + l;
   // where the row of position `pos` starts inside a cache, in units of the cache strides, head offset excluded:
   // contiguous [batch][head][row] caches, or a pool of pages reached through the block table
@@ -160,15 +182,31 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
   const bool to_cache = a.k_cache != nullptr;  // the call appends (as opposed to rotating k in place)
 
   float cs[8], sn[8];
-  if (rotate) {
-    const int n_ang = kNeox ? 8 : 4;
-    const int i0 = kNeox ? 8 * c : 4 * c;
+  {
+    constexpr int kAng = kNeox ? 8 : 4;               // angles of a pair
+    constexpr int kPer = kAng / kRopeSlices;          // angles this thread computes
+    if (rotate) {
+      const int i0 = kNeox ? 8 * c : 4 * c;
 #pragma unroll
-    for (int t = 0; t < 8; ++t) {
-      if (t < n_ang) {
+      for (int u = 0; u < kPer; ++u) {
+        const int t = slice_in * kPer + u;
         const float freq = powf(a.freq_base, -2.0f * static_cast<float>(i0 + t) / static_cast<float>(a.rotary_dim));
         const float ang = static_cast<float>(pos) * freq;
-        sincosf(ang, &sn[t], &cs[t]);
+        float sv, cv;
+        sincosf(ang, &sv, &cv);
+        s_sn[pair][t] = sv;
+        s_cs[pair][t] = cv;
+      }
+    }
+    __syncthreads();
+    if (!valid) return;                               // after the only barrier
+    if (rotate) {
+#pragma unroll
+      for (int t4 = 0; t4 < kAng / 4; ++t4) {
+        const float4 cq = *reinterpret_cast<const float4*>(&s_cs[pair][4 * t4]);
+        const float4 sq = *reinterpret_cast<const float4*>(&s_sn[pair][4 * t4]);
+        cs[4 * t4] = cq.x; cs[4 * t4 + 1] = cq.y; cs[4 * t4 + 2] = cq.z; cs[4 * t4 + 3] = cq.w;
+        sn[4 * t4] = sq.x; sn[4 * t4 + 1] = sq.y; sn[4 * t4 + 2] = sq.z; sn[4 * t4 + 3] = sq.w;
       }
     }
   }
@@ -207,13 +245,13 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
     h = r - n_q - n_k;
     return v_base + 2 * static_cast<size_t>(h) * a.kv_stride[2];
   };
-  const int n_slices = static_cast<int>(gridDim.y);
-  for (int r0 = static_cast<int>(blockIdx.y); r0 < n_rows; r0 += 4 * n_slices) {
-    const uint8_t* src[4];
-    int kind[4], hh[4];
-    uint4 xa[4], xb[4];
+  const int n_slices = static_cast<int>(gridDim.y) * kRopeSlices;
+  for (int r0 = static_cast<int>(blockIdx.y) * kRopeSlices + slice_in; r0 < n_rows; r0 += kRopeRows * n_slices) {
+    const uint8_t* src[kRopeRows];
+    int kind[kRopeRows], hh[kRopeRows];
+    uint4 xa[kRopeRows], xb[kRopeRows];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < kRopeRows; ++j) {
       const int r = r0 + j * n_slices;
       kind[j] = -1;
       if (r < n_rows) {
@@ -226,7 +264,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
       }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < kRopeRows; ++j) {
       if (kind[j] < 0) continue;
       const int h = hh[j];
       if (kind[j] == 2) {  // v: copied into the cache
@@ -297,19 +335,19 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
 cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, bool neox, cudaStream_t stream) {
   const int chunks = a.head_dim / 8;
   const int work_chunks = neox ? chunks - a.rotary_dim / 16 : chunks;
-  const long long threads = static_cast<long long>(a.batch) * a.seq * work_chunks;
-  // Slices over the token's rows (query heads + k heads + v heads): enough of them that the grid is about eight
-  // waves of the three 256-thread blocks an SM holds (with one slice a prefill-sized call is 2.3 waves and a
-  // quarter of the GPU idles through the last one), but no fewer than four rows per thread where there is that much
-  // work (every thread computes the sines and cosines of its chunk's angles once, whatever its number of rows)
+  const long long pairs = static_cast<long long>(a.batch) * a.seq * work_chunks;
+  // A block serves 64 (token, chunk) pairs with four threads each, one per slice of the token's rows (query heads +
+  // k heads + v heads).  Small calls get further slices over gridDim.y, down to one row per thread, so that the
+  // grid still covers the GPU; large ones keep at least four rows per thread (all loads of a step in flight).
   const int n_rows = (a.q != nullptr ? a.n_heads : 0) + (a.k != nullptr ? a.n_kv_heads : 0) +
                      (a.v != nullptr && a.v_cache != nullptr ? a.n_kv_heads : 0);
-  const long long blocks_x = (threads + 255) / 256;
-  long long slices = (8 * 3 * 148 + blocks_x - 1) / blocks_x;
-  const long long max_slices = threads >= 65536 ? (n_rows + 3) / 4 : n_rows;
-  if (slices > max_slices) slices = max_slices;
-  if (slices < 1) slices = 1;
-  const dim3 grid(static_cast<unsigned>((threads + 255) / 256), static_cast<unsigned>(slices));
+  if (pairs > 0x7FFFFFFFll - kRopePairs) return cudaErrorInvalidValue;  // the kernel indexes pairs in 32 bits
+  const long long blocks_x = (pairs + kRopePairs - 1) / kRopePairs;
+  long long slices_y = (8 * 3 * 148 + blocks_x - 1) / blocks_x;
+  const long long max_slices = (pairs >= 65536 ? (n_rows + 3) / 4 : n_rows) / kRopeSlices;
+  if (slices_y > max_slices) slices_y = max_slices;
+  if (slices_y < 1) slices_y = 1;
+  const dim3 grid(static_cast<unsigned>(blocks_x), static_cast<unsigned>(slices_y));
   if (bf16) {
     if (neox) rope_append_kernel<true, true><<<grid, 256, 0, stream>>>(a);
     else rope_append_kernel<true, false><<<grid, 256, 0, stream>>>(a);
