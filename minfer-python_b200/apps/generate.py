@@ -213,8 +213,9 @@ if __name__ == "__main__":
     g = torch.Generator().manual_seed(args.seed)
     prompts = torch.randint(0, args.vocab, (args.batch, args.prompt_len), generator=g).cuda()
     with torch.no_grad():
-        # untimed warm-up (module loads, cuBLAS handles, first-launch set-up), then reset the caches
-        generate(model, prompts[:, :64].contiguous(), 2, False)
+        # untimed warm-up at the full shape (module loads, cuBLAS handles and algorithm choices, the allocator's
+        # blocks, first-launch set-up), then reset the caches
+        generate(model, prompts, 2, False)
         model.lens.zero_()
         ids, stats = generate(model, prompts, args.new_tokens, not args.no_attention_timing, args.cuda_graph)
     stats["first_ids"] = ids[0, :8].tolist()
