@@ -144,7 +144,9 @@ class PeerOutputs:
         self._peers.clear()
         self._bases.clear()
         torch.cuda.synchronize(self.local.device)
+        torch.cuda.ipc_collect()          # consumer side: unmap what was opened from the other ranks
         dist.barrier(group=self.group)
+        torch.cuda.ipc_collect()          # producer side: every consumer has let go of this rank's tensor
 
     def peer_ptrs(self, view: torch.Tensor):
         off = view.data_ptr() - self.local.data_ptr()
