@@ -131,6 +131,14 @@ __device__ long long g_trace[kTraceWords];
 #define P_ACC(stmt) do { } while (0)
 #define P_TL(r, jj, e) do { } while (0)
 #endif
+#if defined(MINFER_ATTN_TRACE) && defined(MINFER_ATTN_TRACE_EPI)
+// tuning builds: the epilogue's phases replace the softmax phases in the accounting words 7..10
+#define P_EPI(stmt) do { if (acc_on) { stmt; } } while (0)
+#define P_SMX(stmt) do { if (acc_on) { acc_c = acc_c2 = clock64(); } } while (0)
+#else
+#define P_EPI(stmt) do { } while (0)
+#define P_SMX(stmt) P_ACC(stmt)
+#endif
 
 __device__ __forceinline__ void report_p(int32_t* status, int site) {
   if (status != nullptr && atomicCAS(status, 0, kStatusWaitTimeout) == 0) {
@@ -711,7 +719,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     uint32_t jt = 0;  // key tiles this slot has processed over the CTA's lifetime
 #ifdef MINFER_ATTN_TRACE
     const bool acc_on = (tid & 127) == 0 && blockIdx.x < kTraceCtas;
-    long long acc_t0 = clock64(), acc_c = 0, acc_first = 0, acc_wait = 0, acc_epi = 0, acc_sched = 0, acc_items = 0, acc_ld = 0, acc_max = 0, acc_exp = 0, acc_resc = 0, acc_c2 = 0, acc_ew = 0, acc_el = 0;
+    long long acc_t0 = clock64(), acc_c = 0, acc_first = 0, acc_wait = 0, acc_epi = 0, acc_sched = 0, acc_items = 0, acc_ld = 0, acc_max = 0, acc_exp = 0, acc_resc = 0, acc_c2 = 0, acc_ew = 0, acc_el = 0; [[maybe_unused]] long long acc_e0 = 0, acc_e1 = 0;
 #endif
 
     for (int k = 0; ok; ++k) {
@@ -771,7 +779,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tc_fence_before();
         mbar_arrive(&bars[kSFree + (kTwoS ? s : 0)]);
         P_TL(s, j, 2);
-        P_ACC(acc_c = clock64(); acc_ld += acc_c - acc_c2);
+        P_SMX(acc_c = clock64(); acc_ld += acc_c - acc_c2);
 
         // ---- masking (tile-uniform decision): mask bytes only for mixed tiles of a dense mask; else only
         // the diagonal and the ragged last tile need it ----
@@ -819,7 +827,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           if (move) m_ref = mx;
           l_run *= alpha;
           if (j > 0) {
-            P_ACC(++acc_resc);
+            P_SMX(++acc_resc);
             // PV(j-1) of this slot must have landed before O is touched
             if (!(ok = mbar_wait(&bars[kODone + s], (jt - 1) & 1u, abort_flag))) { report_p(a.status, 41); break; }
             tc_fence_after();
@@ -836,7 +844,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
 
         P_TL(s, j, 3);
-        P_ACC(acc_c2 = clock64(); acc_max += acc_c2 - acc_c);
+        P_SMX(acc_c2 = clock64(); acc_max += acc_c2 - acc_c);
         // ---- P = exp2(S*c - m*c) -> 16-bit pairs -> tensor memory ----
         // the PV MMAs of this slot's previous tile must have finished reading the P columns
         if (jt > 0 && !(ok = mbar_wait(&bars[kPFree + s], (jt - 1) & 1u, abort_flag))) { report_p(a.status, 44); break; }
@@ -889,7 +897,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           }
         }
         l_run += sum2.x + sum2.y;
-        P_ACC(acc_exp += clock64() - acc_c2);
+        P_SMX(acc_exp += clock64() - acc_c2);
         if constexpr (kMasked) ++jm;
         ++jt;
       }
@@ -918,9 +926,11 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
           uint32_t o[64];
+          P_EPI(acc_e0 = clock64());
           tmem_ld32(tmem_o + h * 64, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
           tmem_ld32(tmem_o + h * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&o[32]));
           tc_wait_ld();
+          P_EPI(acc_e1 = clock64(); acc_ld += acc_e1 - acc_e0);
           if (h == D / 64 - 1) {
             tc_fence_before();
             mbar_arrive(&bars[kOFree + s]);  // the MMA warp may overwrite O_s for the next item
@@ -932,8 +942,10 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             v[e] = pack2<BF16>(__uint_as_float(o[2 * e]) * inv, __uint_as_float(o[2 * e + 1]) * inv);
           // the staging buffer is free once the previous box (this pass's predecessor, or the last
           // one of the previous item) has been read by the TMA unit
+          P_EPI(acc_e0 = clock64(); acc_max += acc_e0 - acc_e1);
           if (lane == 0) bulk_wait_read();
           __syncwarp();
+          P_EPI(acc_e1 = clock64(); acc_exp += acc_e1 - acc_e0);
 #pragma unroll
           for (int c = 0; c < 8; ++c)
             st_shared_v4(stage + lane * 128 + ((c ^ (lane & 7)) << 4), v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
@@ -946,6 +958,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             for (int pr = 0; pr < a.n_peers; ++pr) tma_store_4d(&tm_peers.m[pr], stage, h * 64, c1, c2, c3);
             bulk_commit();
           }
+          P_EPI(acc_resc += clock64() - acc_e1);
         }
       }
       P_ACC(acc_epi += clock64() - acc_c);
