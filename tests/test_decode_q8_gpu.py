@@ -150,3 +150,33 @@ def test_q8_full_length_sequences_at_the_end_of_the_allocation(kerns, D, Lmax):
     torch.cuda.synchronize()
     kd, vd = O.q8_0_dequantize(kq, torch.float16), O.q8_0_dequantize(vq, torch.float16)
     check_close(out, O.decode_oracle(q, kd, vd, lens), f"q8 full length D={D}")
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_decode_q8_random_shapes_equal_the_16bit_decode(kerns, seed):
+    """Random GQA groups (1, 2, 3, 4, 6, 8), both head sizes and dtypes, ragged lengths from 1 key up, scales
+    spread over orders of magnitude: the Q8_0 decode must produce the bits of the 16-bit decode on the
+    dequantised cache (the fragments are built from the raw blocks, K in the order of the 16-bit path)."""
+    g = torch.Generator().manual_seed(100 + seed)
+    D = (64, 128)[seed % 2]
+    dtype = (torch.float16, torch.bfloat16)[(seed // 2) % 2]
+    group = (1, 2, 3, 4, 6, 8, 4, 2)[seed]
+    Hkv = int(torch.randint(1, 4, (1,), generator=g))
+    H = Hkv * group
+    B = int(torch.randint(1, 6, (1,), generator=g))
+    Lmax = 4 * int(torch.randint(8, 700, (1,), generator=g))
+    lens = torch.randint(1, Lmax + 1, (B,), generator=g, dtype=torch.int32)
+    lens[0] = 1
+    q = torch.randn(B, H, 1, D, generator=g).to(dtype)
+    # per-row magnitudes from 1e-3 to 1e+2: block scales then cover five orders of magnitude
+    mag = 10.0 ** (5 * torch.rand(B, Hkv, Lmax, 1, generator=g) - 3)
+    kq = O.q8_0_quantize((mag * torch.randn(B, Hkv, Lmax, D, generator=g)).half())
+    vq = O.q8_0_quantize((mag * torch.randn(B, Hkv, Lmax, D, generator=g)).half())
+    out = torch.full((B, H, 1, D), float("nan"), dtype=dtype, device="cuda")
+    kerns.flash_attn_decode_q8(q.cuda(), kq.cuda(), vq.cuda(), lens.cuda(), out)
+    kd, vd = O.q8_0_dequantize(kq, dtype), O.q8_0_dequantize(vq, dtype)
+    ref16 = torch.full((B, H, 1, D), float("nan"), dtype=dtype, device="cuda")
+    kerns.flash_attn_decode(q.cuda(), kd.cuda(), vd.cuda(), lens.cuda(), ref16)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out, ref16), f"seed {seed}: D={D} {dtype} group={group} B={B} Lmax={Lmax}"
