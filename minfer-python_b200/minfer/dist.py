@@ -121,14 +121,17 @@ class PeerOutputs:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.local = torch.zeros(shape, dtype=dtype, device=device)
+        # one handle per consumer: torch's IPC bookkeeping counts one consumer per exported handle
+        mine = [reduce_tensor(self.local) if r != self.rank else None for r in range(self.world)]
         handles = [None] * self.world
-        dist.all_gather_object(handles, reduce_tensor(self.local), group=group)
+        dist.all_gather_object(handles, mine, group=group)
         self._peers = []          # keeps the mappings alive
         self._bases = []
         my_index = self.local.device.index
-        for r, (rebuild, args) in enumerate(handles):
+        for r in range(self.world):
             if r == self.rank:
                 continue
+            rebuild, args = handles[r][self.rank]
             # Open the peer's IPC handle with THIS rank's device current (argument 6 of torch's rebuild function is
             # the device the storage is opened on): the mapping then belongs to this device's context, peer access
             # to the owner is enabled by the open itself, and no context is created on any other GPU.
