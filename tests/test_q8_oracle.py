@@ -32,3 +32,32 @@ def test_restatement_matches_compiled_reference():
     assert torch.equal(q, O.q8_0_quantize_ref(x))
     assert torch.equal(O.q8_0_dequantize(q, torch.float16), O.q8_0_dequantize_ref(q, torch.float16))
     assert torch.equal(O.q8_0_dequantize(q, torch.float32), O.q8_0_dequantize_ref(q, torch.float32))
+
+
+def test_conversion_free_dequantisation_is_exact():
+    """The decode kernel turns an int8 q and its block scale d into (16-bit type)(q * d) without a conversion
+    instruction.  float16: the byte q ^ 0x80 becomes the mantissa of the half 1024.0 (bits 0x6400 | byte = 1152 + q),
+    1152 is subtracted and one half multiply by d rounds once.  bfloat16: the same in fp32 (0x4B000000 | byte =
+    2^23 + 128 + q), the product q * d is exact there, one rounding to bfloat16.  Restated with numpy / torch for
+    all 256 bytes against every finite fp16 scale of either sign: identical to the reference's dequantisation
+    (csrc/quants/impl.cpp:1153-1166: (half)(q * d) with the product in fp32)."""
+    q = np.arange(-128, 128, dtype=np.int32)
+    byte = (q & 0xFF) ^ 0x80
+    scales = np.arange(0x0000, 0x7C00, dtype=np.uint16)                      # every finite non-negative fp16
+    scales = np.concatenate([scales, scales | 0x8000]).view(np.float16)
+    # float16 route
+    x = (0x6400 | byte).astype(np.uint16).view(np.float16)                     # 1152 + q, exactly
+    qi = x - np.float16(1152.0)
+    assert np.array_equal(qi.astype(np.int32), q)
+    with np.errstate(over="ignore"):
+        got16 = qi[None, :] * scales[:, None]                                  # one fp16 multiply (rounds once)
+        want16 = (q[None, :].astype(np.float32) * scales[:, None].astype(np.float32)).astype(np.float16)
+    assert np.array_equal(got16.view(np.uint16), want16.view(np.uint16))
+    # bfloat16 route
+    xf = (0x4B000000 | byte).astype(np.uint32).view(np.float32)               # 2^23 + 128 + q, exactly
+    qf = xf - np.float32(8388736.0)
+    assert np.array_equal(qf.astype(np.int32), q)
+    some = scales[::37].astype(np.float32)
+    prod = torch.from_numpy(qf[None, :] * some[:, None])                       # exact: 8 bits x 11 bits
+    want = torch.from_numpy(q[None, :].astype(np.float32) * some[:, None])
+    assert torch.equal(prod.bfloat16().view(torch.int16), want.bfloat16().view(torch.int16))
