@@ -71,6 +71,13 @@ def test_invalid_arguments_are_rejected_without_a_device():
     assert L.minfer_attn_decode(ctypes.byref(d), None) == 5           # no workspace
     d.n_heads, d.n_kv_heads = 34, 2
     assert L.minfer_attn_decode(ctypes.byref(d), None) == 2           # group of 17 > 16
+    r = _lib.RopeParams()
+    assert L.minfer_attn_rope_append(ctypes.byref(r), None) == 1      # no tensors at all
+    r.q = 0x1000
+    r.batch, r.seq, r.n_heads, r.head_dim, r.rotary_dim, r.freq_base = 1 << 15, 1 << 13, 8, 128, 128, 10000.0
+    assert L.minfer_attn_rope_append(ctypes.byref(r), None) == 1      # 2^32 (token, chunk) pairs: beyond the 32-bit index
+    r.batch, r.seq, r.rotary_dim = 2, 16, 12
+    assert L.minfer_attn_rope_append(ctypes.byref(r), None) == 1      # rotary_dim not a multiple of 8
     for code in range(0, 6):
         assert len(_lib.strerror(code)) > 0
 
