@@ -57,6 +57,15 @@ constexpr int kTileM = 128;
 constexpr int kTileN = 128;
 constexpr int kBlockBytes = 128 * 128;
 constexpr int kEpiBytes = 32 * 128;  // 32 rows x 64 columns of 16-bit output per softmax warp
+// Staging buffers per softmax warp.  With two, the two 64-column passes of a head_dim-128 epilogue do not wait for
+// each other's TMA read; the 32 KB have to come out of the K/V ring (MINFER_ATTN_STAGES128=3).  Measured, interleaved
+// in one process (burst TFLOP/s at B=4 L=4096 / L=16384 bf16 shard / B=8 L=1024): four stages, one buffer 1194 / 1418 /
+// 750; three stages, one buffer 1113 / 1310 / 721; three stages, two buffers 1107 / 1312 / 722.  The fourth ring stage
+// is worth 7 %, the second buffer nothing: the wait between the passes is not what the epilogue spends its time on.
+#ifndef MINFER_ATTN_EPI_BUFS
+#define MINFER_ATTN_EPI_BUFS 1
+#endif
+constexpr int kEpiBufs = MINFER_ATTN_EPI_BUFS;
 constexpr int kThreads = 384;  // softmax 0 (warps 0-3), softmax 1 (4-7), score MMAs (8), scheduler + TMA (9), PV MMAs (10), idle (11)
 // setmaxnreg split of the 384 x 168 launch allocation: 8 x 208 + 4 x 88 = 12 x 168
 #ifndef MINFER_ATTN_REGS_SOFTMAX
@@ -304,7 +313,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   uint8_t* s_q = smem;                   // [2][kTileBytes]
   uint8_t* s_kv = s_q + 2 * kTileBytes;  // [kStages][kTileBytes]
   uint8_t* s_epi = s_kv + kStages * kTileBytes;  // [8 softmax warps][kEpiBytes] transposing buffers of the epilogue
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_epi + 8 * kEpiBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_epi + 8 * kEpiBufs * kEpiBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* sched_id = reinterpret_cast<volatile int*>(tmem_slot + 4);  // [kSchedRing]
@@ -917,7 +926,7 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       // a 128-byte-swizzled tensor map) and one lane hands the box to the TMA unit; rows past seq_q are
       // clipped by the tensor map.
       {
-        const uint32_t stage = smem_u32(s_epi + warp * kEpiBytes);
+        const uint32_t stage0 = smem_u32(s_epi + warp * kEpiBufs * kEpiBytes);
         const int row0 = q0s + (warp & 3) * 32;  // first row of this warp
         auto pick = [&](int i) { return a.out_pos[0] == i ? it.b : (a.out_pos[1] == i ? heads : row0); };
         const int c1 = pick(1), c2 = pick(2), c3 = pick(3);
@@ -943,7 +952,14 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           // the staging buffer is free once the previous box (this pass's predecessor, or the last
           // one of the previous item) has been read by the TMA unit
           P_EPI(acc_e0 = clock64(); acc_max += acc_e0 - acc_e1);
-          if (lane == 0) bulk_wait_read();
+          // (two buffers: pass h owns buffer h, and only that buffer's previous box - two groups back - must have
+          // been read; head_dim 64 has one pass per item and keeps the single-buffer rule)
+          constexpr bool kTwoBufs = kEpiBufs == 2 && D == 128;
+          const uint32_t stage = stage0 + (kTwoBufs ? (h & 1) * kEpiBytes : 0);
+          if (lane == 0) {
+            if constexpr (kTwoBufs) bulk_wait_read_but<1>();
+            else bulk_wait_read();
+          }
           __syncwarp();
           P_EPI(acc_e1 = clock64(); acc_exp += acc_e1 - acc_e0);
 #pragma unroll
@@ -989,7 +1005,7 @@ cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, con
   constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
   // tiles, epilogue staging, barriers and ring heads, (dense masks) the ring's bit planes, alignment slack:
   // exactly the 227 KB an SM offers for the masked D = 128 form
-  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 8 * kEpiBytes + 512 +
+  constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 8 * kEpiBufs * kEpiBytes + 512 +
                           (kMasked ? kMaskRing * (kMaxTiles / 8) * 4 : 0) + 1024;
   static_assert(smem <= 232448, "shared memory per CTA");
   // set once per device (0 = not yet); atomic because several host threads may drive different devices

@@ -188,6 +188,11 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t smem
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all of this thread's bulk groups have finished READING their shared-memory source
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all but the latest N of this thread's bulk groups have finished reading their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read_but() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
 // all of this thread's bulk groups are complete
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
