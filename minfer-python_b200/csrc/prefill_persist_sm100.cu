@@ -276,10 +276,16 @@ prefill_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                        const __grid_constant__ PeerMaps tm_peers, const PrefillArgs a) {
   constexpr int kDB = D / 64;
   constexpr int kTileBytes = kDB * kBlockBytes;
+  // K/V ring depth.  head_dim 64 (16 KB tiles): 4 / 6 / 8 / 10 stages measure 794 / 798 / 810 / 804 TFLOP/s at B=2
+  // L=8192 - flat beyond two tile pairs; head_dim 128 (32 KB tiles) has room for exactly two pairs, and three stages
+  // cost 7 %.
+#ifndef MINFER_ATTN_STAGES64
+#define MINFER_ATTN_STAGES64 8
+#endif
 #ifndef MINFER_ATTN_STAGES128
 #define MINFER_ATTN_STAGES128 4
 #endif
-  constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
+  constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : MINFER_ATTN_STAGES64;
   constexpr int kRing = kMasked ? kMaskRing : kSchedRing;  // ring entries in use
   // Bit c set: the exponentials of a tile's c-th 32-key chunk use the cubic on the FMA pipes.  At D = 64 the
   // kernel is bound by the special-function unit alone (half the MMA work per exponential) and one chunk of four
@@ -1002,7 +1008,7 @@ template <int D, bool BF16, bool kMasked>
 cudaError_t launch_persist_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                                const CUtensorMap& to, const PeerMaps& peers, PrefillArgs a,
                                cudaStream_t stream) {
-  constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : 8;
+  constexpr int kStages = (D == 128) ? MINFER_ATTN_STAGES128 : MINFER_ATTN_STAGES64;
   // tiles, epilogue staging, barriers and ring heads, (dense masks) the ring's bit planes, alignment slack:
   // exactly the 227 KB an SM offers for the masked D = 128 form
   constexpr size_t smem = static_cast<size_t>(2 + kStages) * (D / 64) * kBlockBytes + 8 * kEpiBufs * kEpiBytes + 512 +
