@@ -289,7 +289,7 @@ typedef struct MinferRopeParams {
   int32_t n_heads;
   int32_t n_kv_heads;
   int32_t head_dim;
-  int32_t rotary_dim;
+  int32_t rotary_dim;     /* <= 128 (MINFER_ATTN_EUNSUPPORTED beyond) */
   int32_t start_pos;
   int32_t max_len;
   int32_t dtype;

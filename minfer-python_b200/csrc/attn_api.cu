@@ -281,6 +281,7 @@ int minfer_attn_rope_append(const MinferRopeParams* p, void* stream) {
   if (p->rotary_dim < 0 || p->rotary_dim > p->head_dim || p->rotary_dim % (p->style == 1 ? 16 : 8) != 0)
     return MINFER_ATTN_EINVAL;
   if (!(p->freq_base > 0.f)) return MINFER_ATTN_EINVAL;
+  if (p->rotary_dim > 128) return MINFER_ATTN_EUNSUPPORTED;  // the launcher's frequency table holds 64 entries
   if (p->q != nullptr && (p->n_heads <= 0 || !aligned16(p->q) || !strides_ok(p->q_stride, 3))) return MINFER_ATTN_EINVAL;
   if ((p->k != nullptr || p->v != nullptr) && (p->n_kv_heads <= 0 || !strides_ok(p->kv_stride, 3)))
     return MINFER_ATTN_EINVAL;

@@ -76,6 +76,7 @@ struct RopeArgs {
   float freq_base;
   const int32_t* block_table;  // paged cache: [batch, table_stride] page indices; cache_stride[0] is then per page
   int32_t page_size, table_stride;
+  float freq[64];           // freq_base ^ (-2 i / rotary_dim) for i < rotary_dim / 2, filled by the launcher
 };
 cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, bool neox, cudaStream_t stream);
 

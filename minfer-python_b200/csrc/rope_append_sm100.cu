@@ -25,13 +25,16 @@
 // Thread mapping: a (token, 16-byte chunk of head_dim) pair (neox: the chunk and its
 // partner chunk) is served by four threads of a block, one per slice of the token's
 // rows (query heads, k heads, v heads; more slices over gridDim.y for small calls).
-// The four compute one (two) of the pair's 4 (8) angles each - powf and sincosf are
-// some 250 instructions per angle, which made the kernel instruction-bound when every
-// thread computed all of them - and share them through shared memory; then each walks
-// its rows four at a time with all loads issued first.
+// The frequencies freq_base^(-2i/rotary_dim) come from a 64-entry table that the
+// launcher computes on the host (they depend on two scalars of the call); the four
+// threads compute one (two) of the pair's 4 (8) sincosf each - about a hundred
+// instructions apiece, which with a powf per angle on top made the kernel
+// instruction-bound when every thread computed all of them - and share them through
+// shared memory; then each walks its rows four at a time with all loads issued first.
 #include "../../include/minfer_attn.h"
 #include "attn_internal.h"
 
+#include <cmath>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -111,8 +114,11 @@ __device__ __forceinline__ void round16(float (&x)[8]) {
 #ifndef MINFER_ATTN_ROPE_MINBLOCKS
 #define MINFER_ATTN_ROPE_MINBLOCKS 4
 #endif
-constexpr int kRopePairs = 64;    // (token, chunk) pairs per 256-thread block
-constexpr int kRopeSlices = 4;    // threads per pair = row slices inside a block (warp-uniform: two warps each)
+#ifndef MINFER_ATTN_ROPE_SLICES
+#define MINFER_ATTN_ROPE_SLICES 4
+#endif
+constexpr int kRopeSlices = MINFER_ATTN_ROPE_SLICES;  // threads per pair = row slices inside a block (warp-uniform)
+constexpr int kRopePairs = 256 / kRopeSlices;         // (token, chunk) pairs per 256-thread block
 
 template <bool BF16, bool kNeox>
 __global__ void __launch_bounds__(kRopePairs * kRopeSlices, MINFER_ATTN_ROPE_MINBLOCKS) rope_append_kernel(const RopeArgs a) {
@@ -184,14 +190,14 @@ __global__ void __launch_bounds__(kRopePairs * kRopeSlices, MINFER_ATTN_ROPE_MIN
   float cs[8], sn[8];
   {
     constexpr int kAng = kNeox ? 8 : 4;               // angles of a pair
+    static_assert(kAng % kRopeSlices == 0, "the angles of a pair are dealt out evenly");
     constexpr int kPer = kAng / kRopeSlices;          // angles this thread computes
     if (rotate) {
       const int i0 = kNeox ? 8 * c : 4 * c;
 #pragma unroll
       for (int u = 0; u < kPer; ++u) {
         const int t = slice_in * kPer + u;
-        const float freq = powf(a.freq_base, -2.0f * static_cast<float>(i0 + t) / static_cast<float>(a.rotary_dim));
-        const float ang = static_cast<float>(pos) * freq;
+        const float ang = static_cast<float>(pos) * a.freq[i0 + t];  // the launcher's table: no powf per thread
         float sv, cv;
         sincosf(ang, &sv, &cv);
         s_sn[pair][t] = sv;
@@ -332,7 +338,27 @@ __global__ void __launch_bounds__(kRopePairs * kRopeSlices, MINFER_ATTN_ROPE_MIN
 
 }  // namespace
 
-cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, bool neox, cudaStream_t stream) {
+cudaError_t launch_rope_append(const RopeArgs& a_in, bool bf16, bool neox, cudaStream_t stream) {
+  RopeArgs a = a_in;
+  // The frequencies depend on (freq_base, rotary_dim) only: computed here, once per change of the two, as the
+  // reference's kernels compute them - the exponent -2 i / rotary_dim rounded to fp32, the power taken of it
+  // (csrc/cuda/il_rope/kernel.cuh:9-39) - with the power itself in double, so the table is within half an ulp.
+  {
+    thread_local float cached_base = 0.f;
+    thread_local int cached_rot = -1;
+    thread_local float table[64];
+    if (a.rotary_dim / 2 > 64) return cudaErrorInvalidValue;
+    if (cached_base != a.freq_base || cached_rot != a.rotary_dim) {
+      for (int i = 0; i < a.rotary_dim / 2; ++i) {
+        const float x = -2.0f * static_cast<float>(i) / static_cast<float>(a.rotary_dim);
+        table[i] = static_cast<float>(std::pow(static_cast<double>(a.freq_base), static_cast<double>(x)));
+      }
+      for (int i = a.rotary_dim / 2; i < 64; ++i) table[i] = 0.f;
+      cached_base = a.freq_base;
+      cached_rot = a.rotary_dim;
+    }
+    for (int i = 0; i < 64; ++i) a.freq[i] = table[i];
+  }
   const int chunks = a.head_dim / 8;
   const int work_chunks = neox ? chunks - a.rotary_dim / 16 : chunks;
   const long long pairs = static_cast<long long>(a.batch) * a.seq * work_chunks;
