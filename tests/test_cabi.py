@@ -78,6 +78,8 @@ def test_invalid_arguments_are_rejected_without_a_device():
     assert L.minfer_attn_rope_append(ctypes.byref(r), None) == 1      # 2^32 (token, chunk) pairs: beyond the 32-bit index
     r.batch, r.seq, r.rotary_dim = 2, 16, 12
     assert L.minfer_attn_rope_append(ctypes.byref(r), None) == 1      # rotary_dim not a multiple of 8
+    r.head_dim, r.rotary_dim = 256, 256
+    assert L.minfer_attn_rope_append(ctypes.byref(r), None) == 2      # more than 64 frequencies: unsupported
     for code in range(0, 6):
         assert len(_lib.strerror(code)) > 0
 
