@@ -30,9 +30,10 @@
 // threads compute one (two) of the pair's 4 (8) sincosf each - about a hundred
 // instructions apiece, which with a powf per angle on top made the kernel
 // instruction-bound when every thread computed all of them - and share them through
-// shared memory; then each walks its rows in batches of six 16-byte chunks that it first
+// shared memory; then each walks its rows in batches whose 16-byte chunks it first
 // brings into shared memory with asynchronous copies, so that no registers are held
-// while the loads are in flight.
+// while the loads are in flight (interleaved form: the next batch flies while this one
+// is worked on).
 #include "../../include/minfer_attn.h"
 #include "attn_internal.h"
 #include "ptx.cuh"
@@ -117,12 +118,14 @@ __device__ __forceinline__ void round16(float (&x)[8]) {
 #ifndef MINFER_ATTN_ROPE_MINBLOCKS
 #define MINFER_ATTN_ROPE_MINBLOCKS 4
 #endif
-#ifndef MINFER_ATTN_ROPE_STAGE_ROWS
-// 16-byte chunks per thread staged in shared memory by asynchronous copies before the thread works through them
-// (0: plain loads into registers, four rows at a time).  Measured on the prefill-sized call (B=4, L=4096, 32/8 heads,
-// D=128; interleaved / two-halves / D=64 interleaved, us): registers 77.7 / 84.1 / 47.4; 6 chunks 72.0 / 70.8 / 42.9;
-// 8 chunks 74.1 / 70.4 / 43.2; 10 chunks 79.2 / 72.2 / 44.7.  A thread has 12 rows there: two even batches of six.
-#define MINFER_ATTN_ROPE_STAGE_ROWS 6
+// Loads staged in shared memory by asynchronous copies before the thread works through them (0: plain loads into
+// registers, four rows at a time).  Measured on the prefill-sized call (B=4, L=4096, 32/8 heads, D=128; interleaved /
+// two-halves / D=64 interleaved, us): registers 77.7 / 84.1 / 47.4; one buffer of 6 chunks 72.0 / 70.9 / 43.0 (8
+// chunks 74.1 / 70.4 / 43.2, 10 chunks 79.2 / 72.2 / 44.7); two buffers of 4 chunks, the next batch in flight while
+// this one is worked on, 67.4 / 78.0 / 41.4 (of 2 chunks 70.0 / 76.0 / 43.2).  The interleaved form therefore uses two
+// buffers of four rows, the two-halves form (two chunks per row, more registers) one buffer of three rows.
+#ifndef MINFER_ATTN_ROPE_STAGED
+#define MINFER_ATTN_ROPE_STAGED 1
 #endif
 #ifndef MINFER_ATTN_ROPE_SLICES
 #define MINFER_ATTN_ROPE_SLICES 4
@@ -325,14 +328,17 @@ __global__ void __launch_bounds__(kRopePairs * kRopeSlices, MINFER_ATTN_ROPE_MIN
   };
   const int n_slices = static_cast<int>(gridDim.y) * kRopeSlices;
   auto wanted = [&](int kd) { return kd == 0 ? do_q : (kd == 1 ? do_k : do_v); };
-#if MINFER_ATTN_ROPE_STAGE_ROWS > 0
+#if MINFER_ATTN_ROPE_STAGED
   // Loads through shared memory: a thread issues the 16-byte asynchronous copies of up to kStageRows of its rows
   // (cp.async, no registers held while they fly), waits for its own copies and then works through the rows.
   constexpr int kNC = kNeox ? 2 : 1;                                    // chunks per row and thread
-  constexpr int kStageRows = MINFER_ATTN_ROPE_STAGE_ROWS / kNC;
-  __shared__ __align__(16) uint4 s_rows[kStageRows * kNC * kRopePairs * kRopeSlices];
+  constexpr int kStageRows = kNeox ? 3 : 4;                             // rows per batch
+  constexpr int kBufs = kNeox ? 1 : 2;                                  // 2: the next batch flies while this one is worked on
+  constexpr int kBatch = kStageRows * kNC * kRopePairs * kRopeSlices;   // uint4 per buffer
+  __shared__ __align__(16) uint4 s_rows[kBufs * kBatch];
   const int tid = static_cast<int>(threadIdx.x);
-  for (int r0 = static_cast<int>(blockIdx.y) * kRopeSlices + slice_in; r0 < n_rows; r0 += kStageRows * n_slices) {
+  const int step = kStageRows * n_slices;
+  auto issue = [&](int r0, int buf) {
 #pragma unroll
     for (int j = 0; j < kStageRows; ++j) {
       const int r = r0 + j * n_slices;
@@ -340,13 +346,24 @@ __global__ void __launch_bounds__(kRopePairs * kRopeSlices, MINFER_ATTN_ROPE_MIN
         int kd, h;
         const uint8_t* srcp = row_of(r, kd, h);
         if (wanted(kd)) {
-          cp_async_16(&s_rows[(j * kNC) * 256 + tid], srcp + co, true);
-          if (kNeox && c2 >= 0) cp_async_16(&s_rows[(j * kNC + kNC - 1) * 256 + tid], srcp + co2, true);
+          cp_async_16(&s_rows[buf * kBatch + (j * kNC) * 256 + tid], srcp + co, true);
+          if (kNeox && c2 >= 0) cp_async_16(&s_rows[buf * kBatch + (j * kNC + kNC - 1) * 256 + tid], srcp + co2, true);
         }
       }
     }
     cp_async_commit();
-    cp_async_wait<0>();
+  };
+  const int first = static_cast<int>(blockIdx.y) * kRopeSlices + slice_in;
+  if (kBufs == 2 && first < n_rows) issue(first, 0);
+  int buf = 0;
+  for (int r0 = first; r0 < n_rows; r0 += step, buf ^= (kBufs - 1)) {
+    if constexpr (kBufs == 2) {
+      issue(r0 + step, buf ^ 1);     // (an empty group when there is no next batch)
+      cp_async_wait<1>();
+    } else {
+      issue(r0, 0);
+      cp_async_wait<0>();
+    }
 #pragma unroll
     for (int j = 0; j < kStageRows; ++j) {
       const int r = r0 + j * n_slices;
@@ -354,8 +371,8 @@ __global__ void __launch_bounds__(kRopePairs * kRopeSlices, MINFER_ATTN_ROPE_MIN
       int kd, h;
       const uint8_t* srcp = row_of(r, kd, h);
       if (!wanted(kd)) continue;
-      const uint4 xa_ = s_rows[(j * kNC) * 256 + tid];
-      const uint4 xb_ = (kNeox && c2 >= 0) ? s_rows[(j * kNC + kNC - 1) * 256 + tid] : make_uint4(0u, 0u, 0u, 0u);
+      const uint4 xa_ = s_rows[buf * kBatch + (j * kNC) * 256 + tid];
+      const uint4 xb_ = (kNeox && c2 >= 0) ? s_rows[buf * kBatch + (j * kNC + kNC - 1) * 256 + tid] : make_uint4(0u, 0u, 0u, 0u);
       process(kd, h, srcp, xa_, xb_);
     }
   }
